@@ -41,10 +41,23 @@ class CacheNeed:
     chunk: int | None = None             # a query sees only the keys of its own chunk of this many positions
     state_shape: tuple[int, ...] = ()    # state per sequence; () for none
     state_dtype: str = "float32"         # "float32" | "bfloat16" | "int32"
+    values_in_keys: bool = False         # a key's value is a part of its key row: the line has no value pages
 
     @property
     def group_key(self) -> tuple | None:
-        return (self.kv_heads, self.head_dim, self.window, self.value_dim or self.head_dim, self.chunk) if self.kv_heads else None
+        if not self.kv_heads:
+            return None
+        return (self.kv_heads, self.head_dim, self.window, 0 if self.values_in_keys else self.value_dim or self.head_dim, self.chunk)
+
+    def shared_with(self, reader: "CacheNeed") -> "CacheNeed":
+        """What a line needs that this need's run writes and a run with need ``reader`` reads as well: the two may
+        differ in their windows only, and the line keeps what the wider one sees (every key if either sees every key)."""
+        from dataclasses import replace
+        if replace(reader, window=self.window) != self:
+            raise ValueError(f"a run that needs {reader} cannot read a cache line written for {self}")
+        if self.window is None or reader.window is None:
+            return replace(self, window=None)
+        return replace(self, window=max(self.window, reader.window))
 
 
 def pages_for(tokens: int) -> int:
@@ -56,7 +69,7 @@ class LineView:
     """What a mixer sees of its cache line."""
 
     keys: torch.Tensor | None            # [num_pages, kv_heads, PAGE_TOKENS, head_dim]
-    values: torch.Tensor | None          # [num_pages, kv_heads, value_dim, PAGE_TOKENS]
+    values: torch.Tensor | None          # [num_pages, kv_heads, value_dim, PAGE_TOKENS]; value_dim 0: values lie in the keys
     page_table: torch.Tensor | None      # int32 [num_slots, max_pages]; -1 where no page is held
     window: int | None
     state: torch.Tensor | None           # [num_slots, *state_shape] in the need's state_dtype

@@ -1,5 +1,6 @@
 from .base import ConfigError, KeyReader, ModelConfig, read_config_json
 from .bamasun import BamasunConfig
+from .depelix import DepelixConfig
 from .fotanex import FotanexConfig
 from .minimax_m2 import MiniMaxM2Config
 from .plan import LayerSpec, ModelPlan, PartSpec, RunSpec, default_run_order
@@ -7,7 +8,7 @@ from .registry import (Architecture, architecture_for, load_config, register_arc
                        registered_architectures)
 
 __all__ = [
-    "Architecture", "BamasunConfig", "ConfigError", "FotanexConfig", "KeyReader", "LayerSpec", "MiniMaxM2Config", "ModelConfig", "ModelPlan",
+    "Architecture", "BamasunConfig", "ConfigError", "DepelixConfig", "FotanexConfig", "KeyReader", "LayerSpec", "MiniMaxM2Config", "ModelConfig", "ModelPlan",
     "PartSpec", "RunSpec", "architecture_for", "default_run_order", "load_config", "read_config_json",
     "register_architecture", "registered_architectures",
 ]

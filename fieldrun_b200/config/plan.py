@@ -28,13 +28,15 @@ class PartSpec:
 class LayerSpec:
     """A layer: a block arrangement over a mixer and a feed-forward, each with its norm (where the norm
     sits, before the sublayer or on its output, is the block's business).  A layer without a feed-forward
-    has ``feed_forward`` and ``feed_forward_norm`` None."""
+    has ``feed_forward`` and ``feed_forward_norm`` None.  ``addition`` names a part that adds to the stream once more
+    after the block (category ``addition``: a further input per layer that reads the stream and the step's tokens)."""
 
     block: str
     mixer: PartSpec
     feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
     feed_forward_norm: Optional[PartSpec]
+    addition: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

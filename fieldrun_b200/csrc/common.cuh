@@ -161,6 +161,17 @@ __device__ __forceinline__ void block_sum_pair(float& a, float& b, float* scratc
     b = scratch[32];
 }
 
+// The gate of a feed-forward unit with two products in: silu(gate) * up, or, with a positive `limit`, the clamped form
+// g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1).
+#define FRB_CLAMPED_GATE_SLOPE 1.702f
+__device__ __forceinline__ float paired_gate(float gate, float up, float limit) {
+    if (limit > 0.f) {
+        const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+        return g / (1.0f + expf(-FRB_CLAMPED_GATE_SLOPE * g)) * (u + 1.0f);
+    }
+    return gate / (1.0f + expf(-gate)) * up;
+}
+
 // Calls `body` with a value of the element type that `code` names.
 #define FRB_DISPATCH_DTYPE(code, T, ...)                          \
     do {                                                          \

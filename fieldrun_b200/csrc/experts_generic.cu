@@ -2,7 +2,8 @@
 // It is the expert path of the float32 model and the fallback of the bfloat16 model for sizes the
 // tensor-core kernels refuse.
 //
-// PAIRED: h = silu(x W1^T) * (x W3^T) with W = [E][2F][K] holding the F gate rows then the F up rows;
+// PAIRED: h = silu(x W1^T) * (x W3^T) with W = [E][2F][K] holding the F gate rows then the F up rows (with a positive
+// gate_limit the clamped gate of common.cuh's paired_gate instead);
 // otherwise y = x W^T with W = [E][F][K]  (src/minimax.rs:116-120; silu(x) = x/(1+exp(-x)), :31).
 #include "common.cuh"
 
@@ -15,7 +16,7 @@ __global__ void __launch_bounds__(256)
 expert_gemm_generic_kernel(const T* __restrict__ W, const T* __restrict__ X, const int* __restrict__ x_rows,
                            const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                            const int* __restrict__ num_tiles, const int* __restrict__ offsets, OutT* __restrict__ out,
-                           int F, int K) {
+                           int F, int K, float gate_limit) {
     __shared__ float xs[EG_K][EG_ROWS + 1];
     __shared__ float wg[EG_K][EG_FEATS + 1];
     __shared__ float wu[PAIRED ? EG_K : 1][EG_FEATS + 1];
@@ -80,7 +81,7 @@ expert_gemm_generic_kernel(const T* __restrict__ W, const T* __restrict__ X, con
             const int f = f0 + tx * 4 + j;
             if (f >= F) continue;
             float v = acc_g[i][j];
-            if (PAIRED) v = v / (1.0f + expf(-v)) * acc_u[i][j];
+            if (PAIRED) v = paired_gate(v, acc_u[i][j], gate_limit);
             out[(size_t)(row0 + r) * F + f] = from_f32<OutT>(v);
         }
     }
@@ -90,13 +91,13 @@ expert_gemm_generic_kernel(const T* __restrict__ W, const T* __restrict__ X, con
 // max_tiles bounds the grid; blocks beyond num_tiles[0] leave at once.
 FRB_API int frb_expert_gemm_generic(const void* W, const void* X, int dtype, const int* x_rows, const int* tile_expert,
                                     const int* tile_row0, const int* num_tiles, const int* offsets, int max_tiles,
-                                    void* out, int out_dtype, int F, int K, int paired, cudaStream_t stream) {
+                                    void* out, int out_dtype, int F, int K, int paired, float gate_limit, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     dim3 grid(max_tiles, (F + EG_FEATS - 1) / EG_FEATS);
     FRB_CHECK_ARG(grid.y <= 65535, "expert product: %d features exceed the grid", F);
 #define LAUNCH(T, OutT, P)                                                                                              \
     expert_gemm_generic_kernel<T, OutT, P><<<grid, 256, 0, stream>>>((const T*)W, (const T*)X, x_rows, tile_expert,      \
-                                                                     tile_row0, num_tiles, offsets, (OutT*)out, F, K)
+                                                                     tile_row0, num_tiles, offsets, (OutT*)out, F, K, gate_limit)
     FRB_DISPATCH_DTYPE(dtype, T, FRB_DISPATCH_DTYPE(out_dtype, OutT, {
         if (paired) LAUNCH(T, OutT, true); else LAUNCH(T, OutT, false);
     }));

@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(512 / NB)
 expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, const int* __restrict__ x_rows,
                        const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                        const int* __restrict__ num_tiles, const int* __restrict__ offsets, OutT* __restrict__ out, int F, int K,
-                       int k_per_split, int groups) {
+                       int k_per_split, int groups, float gate_limit) {
     after_previous_kernel();
     extern __shared__ float partial[];       // [splits - 1][groups][NACC][32]
     constexpr int NACC = NB * 4 * (PAIRED ? 2 : 1);
@@ -137,7 +137,7 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
             if (r >= rows) continue;
             const int f = f0 + g + 8 * (i >> 1);
             float v = acc_g[j][i];
-            if (PAIRED) v = v / (1.0f + expf(-v)) * acc_u[j][i];
+            if (PAIRED) v = paired_gate(v, acc_u[j][i], gate_limit);
             out[(size_t)(row0 + r) * F + f] = from_f32<OutT>(v);
         }
     }
@@ -149,7 +149,7 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
 // 16 features a block takes (4 when there are many tiles).
 FRB_API int frb_expert_gemm_mma(const void* W, const void* X, const int* x_rows, const int* tile_expert, const int* tile_row0,
                                 const int* num_tiles, const int* offsets, int max_tiles, int tile_rows, void* out, int F, int K,
-                                int paired, int splits, int groups, cudaStream_t stream) {
+                                int paired, int splits, int groups, float gate_limit, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     FRB_CHECK_ARG(K % 32 == 0 && K > 0, "expert stream: inner size %d is not a multiple of 32", K);
     FRB_CHECK_ARG(F % 16 == 0 && F > 0, "expert stream: %d features are not a multiple of 16", F);
@@ -166,10 +166,10 @@ FRB_API int frb_expert_gemm_mma(const void* W, const void* X, const int* x_rows,
 #define LAUNCH(NB)                                                                                                        \
     if (paired)                                                                                                           \
         launch_dependent(expert_gemm_mma_kernel<NB, true, bf16>, dim3(grid), dim3(threads), smem, stream,                                           \
-            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (bf16*)out, F, K, k_per_split, groups); \
+            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (bf16*)out, F, K, k_per_split, groups, gate_limit); \
     else                                                                                                                  \
         launch_dependent(expert_gemm_mma_kernel<NB, false, float>, dim3(grid), dim3(threads), smem, stream,                                         \
-            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (float*)out, F, K, k_per_split, groups)
+            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (float*)out, F, K, k_per_split, groups, gate_limit)
     if (tile_rows == 8) { LAUNCH(1); } else if (tile_rows == 16) { LAUNCH(2); } else { LAUNCH(4); }
 #undef LAUNCH
     FRB_RETURN_LAUNCH("expert_gemm_mma");

@@ -58,6 +58,7 @@ struct StreamParams {
     void* out;
     int* status;              // 0, or the code of the wait that gave up
     int F, K;
+    float gate_limit;         // paired products: 0 silu(gate) * up, > 0 the clamped gate (paired_gate)
     int groups_per_tile;      // items of sixteen weight rows per tile: F / 8 for a pair, else F / 16
     int groups_per_expert;    // from one expert's first item to the next expert's, in the map's last coordinate
     int pieces;               // pieces of 64 k per stage
@@ -247,7 +248,7 @@ weight_stream_kernel(const __grid_constant__ CUtensorMap map_w, StreamParams p) 
                             if (r >= rows) continue;
                             if (PAIRED) {
                                 const float gate = sum[j][i], up = sum[j][i + 2];
-                                out[(size_t)(row0 + r) * p.F + group * 8 + weight_row] = from_f32<OutT>(gate / (1.0f + expf(-gate)) * up);
+                                out[(size_t)(row0 + r) * p.F + group * 8 + weight_row] = from_f32<OutT>(paired_gate(gate, up, p.gate_limit));
                             } else {
                                 out[(size_t)(row0 + r) * p.F + group * 16 + weight_row + 8 * (i >> 1)] = from_f32<OutT>(sum[j][i]);
                             }
@@ -268,7 +269,7 @@ weight_stream_kernel(const __grid_constant__ CUtensorMap map_w, StreamParams p) 
 FRB_API int frb_weight_stream(const void* W, int num_experts, const void* X, const int* x_rows, const int* tile_expert,
                               const int* tile_row0, const int* num_tiles, const int* offsets, int max_tiles, int tile_rows,
                               void* out, int F, int K, int paired, int lists_final, int blocks, int ring_kb, int pieces, int* status,
-                              cudaStream_t stream) {
+                              float gate_limit, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     FRB_CHECK_ARG(K % WS_PIECE_K == 0 && K > 0, "weight stream: inner size %d is not a multiple of 64", K);
     FRB_CHECK_ARG(F > 0 && F % (paired ? 8 : 16) == 0, "weight stream: %d features are not a multiple of %d", F, paired ? 8 : 16);
@@ -277,7 +278,7 @@ FRB_API int frb_weight_stream(const void* W, int num_experts, const void* X, con
     FRB_CHECK_ARG(blocks > 0 && ring_kb >= 16 && ring_kb <= 200, "weight stream: %d blocks with a ring of %d KB", blocks, ring_kb);
     StreamParams p;
     p.X = (const bf16*)X; p.x_rows = x_rows; p.tile_expert = tile_expert; p.tile_row0 = tile_row0; p.num_tiles = num_tiles;
-    p.offsets = offsets; p.out = out; p.status = status; p.F = F; p.K = K; p.lists_final = lists_final;
+    p.offsets = offsets; p.out = out; p.status = status; p.F = F; p.K = K; p.lists_final = lists_final; p.gate_limit = gate_limit;
     p.groups_per_tile = paired ? F / 8 : F / 16;
     p.groups_per_expert = paired ? 2 * F / 8 : F / 16;
     // pieces per stage: as many as divide the inner size evenly, so that no stage is half empty; sixteen if none does

@@ -32,6 +32,7 @@ struct TcParams {
     void* out;
     int* status;             // 0, or the code of the wait that gave up
     int F, K, NT, stages, tmem_cols;
+    float gate_limit;        // PAIRED kernels: 0 silu(gate) * up, > 0 the clamped gate
     int activation;          // ACTIVE kernels: 0 relu(z)^2, 1 tanh-gelu, 2 silu, 3 relu, applied to a plain product's result
 };
 
@@ -181,7 +182,15 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                         if (n < rows) {
                             float v = __uint_as_float(gate[half][j]);
                             // silu(gate) * up; the result is rounded to bfloat16, so the fast exponential and division do
-                            if (PAIRED) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(up[half][j]);
+                            if (PAIRED) {
+                                const float u = __uint_as_float(up[half][j]);
+                                if (p.gate_limit > 0.f) {
+                                    const float g = fminf(v, p.gate_limit), uc = fminf(fmaxf(u, -p.gate_limit), p.gate_limit);
+                                    v = __fdividef(g, 1.0f + __expf(-FRB_CLAMPED_GATE_SLOPE * g)) * (uc + 1.0f);
+                                } else {
+                                    v = __fdividef(v, 1.0f + __expf(-v)) * u;
+                                }
+                            }
                             if (ACTIVE) v = unit_activation(v, p.activation);
                             out[(size_t)(row0 + n) * p.F + f] = from_f32<OutT>(v);
                             if (WIDE) {
@@ -217,7 +226,7 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // order); tiles of tile_rows = 32, 64, 128 or 256 rows.  status: one int on the device, zero before the call.
 FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, int x_rows_total, const int* tile_expert,
                                const int* tile_row0, const int* num_tiles, const int* offsets, int max_tiles, int tile_rows,
-                               void* out, int F, int K, int paired, int* status, int activation, cudaStream_t stream) {
+                               void* out, int F, int K, int paired, int* status, int activation, float gate_limit, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     FRB_CHECK_ARG(activation >= -1 && activation <= 3 && !(paired && activation >= 0),
                   "expert tensor-core product: activation %d (none is -1; a paired product has its gate)", activation);
@@ -232,7 +241,7 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
                   "expert tensor-core product: cuTensorMapEncodeTiled failed or is not available");
     TcParams p;
     p.tile_expert = tile_expert; p.tile_row0 = tile_row0; p.num_tiles = num_tiles; p.offsets = offsets; p.out = out;
-    p.status = status; p.F = F; p.K = K; p.NT = tile_rows; p.activation = activation;
+    p.status = status; p.F = F; p.K = K; p.NT = tile_rows; p.activation = activation; p.gate_limit = gate_limit;
     // products of one matrix take 256 features a block where the tiles are large and arithmetic is the bound
     const bool wide = !paired && tile_rows >= 128 && F % (2 * TC_FEATS) == 0;
     const bool two = paired || wide;

@@ -44,7 +44,7 @@ _SIGNATURES = {
     "frb_router_topk": "ppiiiifpp",
     "frb_expert_plan": "piiiippppppp",
     "frb_expert_combine": "pppiiip",
-    "frb_expert_gemm_generic": "ppipppppipiiii",
+    "frb_expert_gemm_generic": "ppipppppipiiiif",
     "frb_sample_rows": "piipppp",
     "frb_argmax_rows": "piippp",
     "frb_sample_floor": "piippppppp",
@@ -52,14 +52,23 @@ _SIGNATURES = {
     "frb_attention_decode_mma": "ppppipppppiiiifiippip",
     "frb_attention_prefill_mma": "ppppippipppppiiifipip",
     "frb_attention_decode_tma": "pppipipppppiiiifiiippip",
-    "frb_expert_gemm_mma": "pppppppiipiiiii",
-    "frb_weight_stream": "pippppppiipiiiiiiip",
+    "frb_expert_gemm_mma": "pppppppiipiiiiif",
+    "frb_weight_stream": "pippppppiipiiiiiiipf",
     "frb_route_plan_small": "ppiiiifipppppppp",
     "frb_router_small": "ppipppiiiifipppppppp",
     "frb_router_logits": "ppiiip",
-    "frb_expert_gemm_tc": "pipippppiipiiipi",
+    "frb_expert_gemm_tc": "pipippppiipiiipif",
     "frb_gather_rows_bf16": "pppii",
     "frb_attention_prefill_tc": "pippipippipppppiiifippip",
+    "frb_embed_pair_rows": "pppipiiifillppppppi",
+    "frb_token_side_gate": "pppipiiiiii",
+    "frb_add_rms_normed": "pppiif",
+    "frb_add_typed_copy": "pppil",
+    "frb_scaled_rows": "pipppiiii",
+    "frb_latent_prepare": "piiiiiippfppipppippii",
+    "frb_latent_queries": "pppippipiiiiii",
+    "frb_latent_attention": "pppipipppiiiifi",
+    "frb_latent_gate": "ppiiipiiii",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -72,11 +81,13 @@ class KernelError(RuntimeError):
 _ENTRY_GROUPS = {
     "common": ("frb_embed_rows", "frb_rmsnorm", "frb_qkv_prepare", "frb_add_rows", "frb_attention_generic", "frb_layernorm",
                "frb_unary_unit", "frb_softcap", "frb_gated_unit", "frb_sample_rows", "frb_argmax_rows", "frb_sample_floor",
-               "frb_dyt_norm", "frb_rms_blend", "frb_concat_rows", "frb_add_row_vector", "frb_head_gate"),
+               "frb_dyt_norm", "frb_rms_blend", "frb_concat_rows", "frb_add_row_vector", "frb_head_gate", "frb_embed_pair_rows",
+               "frb_token_side_gate", "frb_add_rms_normed", "frb_add_typed_copy"),
+    "latent": ("frb_latent_prepare", "frb_latent_queries", "frb_latent_attention", "frb_latent_gate"),
     "attention": ("frb_attention_decode_mma", "frb_attention_prefill_mma", "frb_attention_decode_tma", "frb_attention_prefill_tc"),
     "streams": ("frb_weight_stream", "frb_expert_gemm_mma"),
     "experts": ("frb_router_topk", "frb_expert_plan", "frb_expert_combine", "frb_expert_gemm_generic", "frb_route_plan_small",
-                "frb_router_small", "frb_router_logits"),
+                "frb_router_small", "frb_router_logits", "frb_scaled_rows"),
     "products": ("frb_expert_gemm_tc", "frb_gather_rows_bf16"),
     "recurrent": ("frb_gla_scan",),
     "scans": ("frb_causal_conv", "frb_softplus_bias", "frb_selective_scan", "frb_gated_recurrence", "frb_state_space_scan", "frb_group_rms_norm"),
@@ -646,13 +657,15 @@ def expert_combine(y: torch.Tensor, weights: torch.Tensor, row_of_assign: torch.
 
 def expert_gemm_generic(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
                         tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
-                        out: torch.Tensor, *, paired: bool) -> None:
-    """out[row] = silu(x W1^T) * (x W3^T) (paired; w is [E, 2F, K]) or x W^T (w is [E, F, K]) per sorted row."""
+                        out: torch.Tensor, *, paired: bool, gate_limit: float = 0.0) -> None:
+    """out[row] = silu(x W1^T) * (x W3^T) (paired; w is [E, 2F, K]) or x W^T (w is [E, F, K]) per sorted row.
+    ``gate_limit`` > 0 (here and in the other expert products): the paired form is the clamped gate instead,
+    g = min(x W1^T, limit), u = clamp(x W3^T, -limit, limit), g sigmoid(1.702 g) (u + 1)."""
     if w.dtype != x.dtype:
         raise KernelError("expert weights and their input must have one dtype")
     feats = w.shape[1] // 2 if paired else w.shape[1]
     _call("frb_expert_gemm_generic", _ptr(w), _ptr(x), _code(w.dtype), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0),
-          _ptr(num_tiles), _ptr(offsets), max_tiles, _ptr(out), _code(out.dtype), feats, w.shape[2], int(paired))
+          _ptr(num_tiles), _ptr(offsets), max_tiles, _ptr(out), _code(out.dtype), feats, w.shape[2], int(paired), float(gate_limit))
 
 
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
@@ -814,7 +827,8 @@ def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
 
 def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
                     tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
-                    tile_rows: int, out: torch.Tensor, *, paired: bool, splits: int = 1, groups: int = 4) -> None:
+                    tile_rows: int, out: torch.Tensor, *, paired: bool, splits: int = 1, groups: int = 4,
+                    gate_limit: float = 0.0) -> None:
     """The expert products as a stream over bfloat16 weights (tiles of 8, 16 or 32 rows; per block ``groups``
     groups of 16 features and ``splits`` parts of the inner size; see :func:`stream_shape`)."""
     _want(w, torch.bfloat16, "streamed expert weights")
@@ -822,7 +836,7 @@ def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Ten
     _want(out, torch.bfloat16 if paired else torch.float32, "streamed expert outputs")
     feats = w.shape[1] // 2 if paired else w.shape[1]
     _call("frb_expert_gemm_mma", _ptr(w), _ptr(x), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
-          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), int(splits), int(groups))
+          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), int(splits), int(groups), float(gate_limit))
 
 
 import os as _os
@@ -838,7 +852,7 @@ def weight_stream_takes(features: int, inner: int, paired: bool) -> bool:
 def weight_stream(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
                   tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
                   tile_rows: int, out: torch.Tensor, *, paired: bool, lists_final: bool = False,
-                  blocks: Optional[int] = None, ring_kb: Optional[int] = None, pieces: int = 0) -> None:
+                  blocks: Optional[int] = None, ring_kb: Optional[int] = None, pieces: int = 0, gate_limit: float = 0.0) -> None:
     """Products of a few rows with bfloat16 weights [E, F or 2F, K] as one stream over the weights per SM: TMA into
     a ring of stages, ``mma.sync`` from shared memory (tiles of 8, 16 or 32 rows).  ``lists_final``: the lists of
     tiles were complete before the kernel before this one in the stream began (a dense layer's fixed lists; the
@@ -850,7 +864,7 @@ def weight_stream(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tenso
     _call("frb_weight_stream", _ptr(w), w.shape[0], _ptr(x), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0),
           _ptr(num_tiles), _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired),
           int(lists_final), int(blocks or sm_count(w.device)), int(ring_kb or STREAM_RING_KB), int(pieces or STREAM_PIECES),
-          _ptr(tc_status(w.device)))
+          _ptr(tc_status(w.device)), float(gate_limit))
 
 
 SMALL_ROUTE_ASSIGNMENTS = 1024
@@ -952,7 +966,7 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 
 def expert_gemm_tc(w: torch.Tensor, x: torch.Tensor, tile_expert: torch.Tensor, tile_row0: torch.Tensor,
                    num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int, tile_rows: int, out: torch.Tensor, *,
-                   paired: bool, activation: Optional[str] = None) -> None:
+                   paired: bool, activation: Optional[str] = None, gate_limit: float = 0.0) -> None:
     """The expert products on tcgen05 tensor cores; x holds the rows in expert-sorted order (tiles of 32, 64,
     128 or 256 rows; features in steps of 128, inner size in steps of 64).  A plain product may send its result
     through an ``activation`` (a key of ``ACTIVATIONS``) on the way out, in bfloat16: the first half of a dense
@@ -965,7 +979,7 @@ def expert_gemm_tc(w: torch.Tensor, x: torch.Tensor, tile_expert: torch.Tensor, 
     feats = w.shape[1] // 2 if paired else w.shape[1]
     _call("frb_expert_gemm_tc", _ptr(w), w.shape[0], _ptr(x), x.shape[0], _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
           _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), _ptr(tc_status(w.device)),
-          ACTIVATIONS[activation] if activation is not None else -1)
+          ACTIVATIONS[activation] if activation is not None else -1, float(gate_limit))
 
 
 _ROUTER_TICKETS: dict[str, torch.Tensor] = {}
@@ -1019,3 +1033,119 @@ def wait_probe(device, limit_cycles: int = 100_000) -> int:
     with torch.cuda.device(device):
         _call("frb_wait_probe", int(limit_cycles), _ptr(tc_status(device)), _ptr(waited))
     return int(waited.item())
+
+
+# ------------------------------------------------------------------------------------------------ token inputs
+
+def embed_pair_rows(tokens: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor, out: torch.Tensor, *, buckets: int,
+                    mul_prev: int, mul_cur: int, tok_pos: torch.Tensor, tok_seq: torch.Tensor, tok_slot: torch.Tensor,
+                    cu_q_len: torch.Tensor, state: torch.Tensor, scale: float = 1.0, act: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[tokens[t]] * scale + pair_table[row], row = (previous * mul_prev + tokens[t] * mul_cur) mod buckets,
+    or ``buckets`` (the table's extra last row) for a sequence's first token.  ``state`` (int32 [slots, 2]) carries the
+    last token from step to step: a step that begins at position p reads copy p & 1 and writes copy (p + n) & 1."""
+    _want(tokens, torch.int32, "tokens")
+    _want(out, torch.float32, "the residual stream")
+    _want(state, torch.int32, "the previous tokens")
+    if pair_table.dtype != table.dtype or pair_table.shape != (buckets + 1, table.shape[1]):
+        raise KernelError(f"a pair table of shape {list(pair_table.shape)} ({pair_table.dtype}) for {buckets} hashed rows of "
+                          f"{table.shape[1]} ({table.dtype})")
+    if state.dim() != 2 or state.shape[1] != 2 or not state.is_contiguous():
+        raise KernelError("the previous tokens are an int32 pair per slot")
+    vocab, width = table.shape
+    _call("frb_embed_pair_rows", _ptr(tokens), _ptr(table), _ptr(pair_table), _code(table.dtype), _ptr(out), tokens.numel(),
+          width, vocab, float(scale), int(buckets), int(mul_prev), int(mul_cur), _ptr(tok_pos), _ptr(tok_seq), _ptr(tok_slot),
+          _ptr(cu_q_len), _ptr(state), _ptr(act), _code(act.dtype) if act is not None else 0)
+
+
+def token_side_gate(lin: torch.Tensor, tokens: torch.Tensor, side: torch.Tensor, column0: int, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(lin[t, j]) * side[tokens[t], column0 + j]."""
+    _want(lin, torch.float32, "the gate's product")
+    _want(tokens, torch.int32, "tokens")
+    rows, dim = lin.shape
+    _call("frb_token_side_gate", _ptr(lin), _ptr(tokens), _ptr(side), _code(side.dtype), _ptr(out), _code(out.dtype), rows, dim,
+          side.shape[1], int(column0), side.shape[0])
+
+
+def add_rms_normed(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight, in place, all float32."""
+    _want(x, torch.float32, "the residual stream")
+    _want(y, torch.float32, "the update")
+    _want(weight, torch.float32, "the norm's weight")
+    _call("frb_add_rms_normed", _ptr(x), _ptr(y), _ptr(weight), x.shape[0], x.shape[1], float(eps))
+
+
+def add_typed_copy(x: torch.Tensor, delta: Optional[torch.Tensor], act: torch.Tensor) -> None:
+    """x += delta (if given), act = x in act's type."""
+    _want(x, torch.float32, "the residual stream")
+    if delta is not None:
+        _want(delta, torch.float32, "the residual update")
+    _call("frb_add_typed_copy", _ptr(x), _ptr(delta), _ptr(act), _code(act.dtype), x.numel())
+
+
+def scaled_rows(x: torch.Tensor, weights: torch.Tensor, row_of_assign: torch.Tensor, out: torch.Tensor) -> None:
+    """out[row_of_assign[t * k + r]] = weights[t, r] * x[t]: each (token, rank) gets its own row, scaled, in sorted order."""
+    _want(weights, torch.float32, "expert weights")
+    _want(row_of_assign, torch.int32, "rows of the assignments")
+    tokens, top_k = weights.shape
+    _call("frb_scaled_rows", _ptr(x), _code(x.dtype), _ptr(weights), _ptr(row_of_assign), _ptr(out), _code(out.dtype),
+          tokens * top_k, top_k, x.shape[-1])
+
+
+# ------------------------------------------------------------------------------------------------ latent attention
+
+def latent_prepare(down: torch.Tensor, q_weight: torch.Tensor, kv_weight: Optional[torch.Tensor], eps: float,
+                   cos_table: Optional[torch.Tensor], sin_table: Optional[torch.Tensor], tok_pos: torch.Tensor,
+                   tok_slot: torch.Tensor, page_table: Optional[torch.Tensor], cq_out: torch.Tensor,
+                   k_pages: Optional[torch.Tensor], *, q_rank: int, kv_rank: int, rot_dim: int, rotary_dims: int,
+                   interleaved: bool) -> None:
+    """From the float32 rows ``down`` = [query latent | key/value latent | key part | ...]: both latents through their RMS
+    norms, the key part rotated at the token's position, the key row [latent ; part] into its page.  ``kv_weight`` None:
+    the rows hold no key/value latent and nothing is written to the cache."""
+    _want(down, torch.float32, "the down projections")
+    _want(q_weight, torch.float32, "the query latent's norm weight")
+    if kv_weight is not None:
+        _want(kv_weight, torch.float32, "the latent's norm weight")
+        if k_pages is None or page_table is None:
+            raise KernelError("a layer with latents of its own needs a cache line")
+        if k_pages.dtype != cq_out.dtype or k_pages.shape[-1] != kv_rank + rot_dim or k_pages.shape[-3] != 1:
+            raise KernelError(f"key pages of shape {list(k_pages.shape)} for rows of {kv_rank} + {rot_dim}")
+    table_positions = cos_table.shape[0] if cos_table is not None else 0
+    _call("frb_latent_prepare", _ptr(down), down.stride(0), q_rank, kv_rank, rot_dim, rotary_dims, int(interleaved),
+          _ptr(q_weight), _ptr(kv_weight), float(eps), _ptr(cos_table), _ptr(sin_table), table_positions, _ptr(tok_pos),
+          _ptr(tok_slot), _ptr(page_table), page_table.shape[1] if page_table is not None else 0, _ptr(cq_out),
+          _ptr(k_pages), _code(cq_out.dtype), down.shape[0])
+
+
+def latent_queries(q: torch.Tensor, plain: torch.Tensor, rotated: torch.Tensor, cos_table: Optional[torch.Tensor],
+                   sin_table: Optional[torch.Tensor], tok_pos: torch.Tensor, *, heads: int, dim: int, rot_dim: int,
+                   rotary_dims: int, interleaved: bool) -> None:
+    """q float32 [T, heads * (dim + rot_dim)] -> plain [heads, T, dim] and rotated [T, heads, rot_dim] (rotated at the
+    token's position), both in the model type."""
+    _want(q, torch.float32, "the queries")
+    if plain.dtype != rotated.dtype:
+        raise KernelError("both parts of the queries have one dtype")
+    table_positions = cos_table.shape[0] if cos_table is not None else 0
+    _call("frb_latent_queries", _ptr(q), _ptr(plain), _ptr(rotated), _code(plain.dtype), _ptr(cos_table), _ptr(sin_table),
+          table_positions, _ptr(tok_pos), q.shape[0], heads, dim, rot_dim, rotary_dims, int(interleaved))
+
+
+def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Tensor, page_table: torch.Tensor,
+                     tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int, rank: int,
+                     rot_dim: int, scale: float, window: Optional[int]) -> None:
+    """Attention over shared key rows [latent ; rotated part]: q_lat [heads, T, rank], q_rot [T, heads, rot_dim], out
+    [heads, T, rank] = sum of softmax weights times the keys' latents.  Float32 arithmetic, any sizes."""
+    if not (q_lat.dtype == q_rot.dtype == k_pages.dtype == out.dtype):
+        raise KernelError("queries, cache and output must have one dtype")
+    _call("frb_latent_attention", _ptr(q_lat), _ptr(q_rot), _ptr(k_pages), _code(q_lat.dtype), _ptr(page_table),
+          page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q_rot.shape[0], num_heads, rank, rot_dim,
+          float(scale), int(window or 0))
+
+
+def latent_gate(o: torch.Tensor, gate: torch.Tensor, gate_column: int, per_head: bool, out: torch.Tensor, *, heads: int,
+                vdim: int) -> None:
+    """out[t, h * vdim + j] = o[h, t, j] * sigmoid(g), g = gate[t, gate_column + h] (``per_head``) or
+    gate[t, gate_column + h * vdim + j]."""
+    _want(o, torch.float32, "the heads' outputs")
+    _want(gate, torch.float32, "the gate's product")
+    _call("frb_latent_gate", _ptr(o), _ptr(gate), gate.stride(0), int(gate_column), int(per_head), _ptr(out), _code(out.dtype),
+          out.shape[0], heads, vdim)

@@ -687,3 +687,33 @@ FRB_API int frb_expert_combine(const float* y, const float* weights, const int* 
     launch_dependent(combine_kernel, dim3(grid), dim3(256), 0, stream, y, weights, row_of_assign, top_k, width, out);
     FRB_RETURN_LAUNCH("expert_combine");
 }
+
+// ----------------------------------------------------------------------------- rows scaled on the way in
+//
+// out[row_of_assign[a]] = weights[a] * x[a / top_k]: every (token, rank) gets a row of its own in expert-sorted order,
+// the token's row times the weight of that expert.  For experts whose weight belongs on their input (the unit is not
+// linear, so it cannot be applied to the output instead).  The product is made in float32 and rounded once.
+template <typename InT, typename OutT>
+__global__ void scaled_rows_kernel(const InT* __restrict__ x, const float* __restrict__ weights,
+                                   const int* __restrict__ row_of_assign, OutT* __restrict__ out, int assignments, int top_k,
+                                   int width) {
+    after_previous_kernel();
+    for (int a = blockIdx.x; a < assignments; a += gridDim.x) {
+        const float w = weights[a];
+        const InT* src = x + (size_t)(a / top_k) * width;
+        OutT* dst = out + (size_t)row_of_assign[a] * width;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<OutT>(to_f32<InT>(src[i]) * w);
+    }
+}
+
+FRB_API int frb_scaled_rows(const void* x, int x_dtype, const float* weights, const int* row_of_assign, void* out,
+                            int out_dtype, int assignments, int top_k, int width, cudaStream_t stream) {
+    if (assignments == 0) return 0;
+    FRB_CHECK_ARG(top_k >= 1, "scaled rows: %d experts a token", top_k);
+    const dim3 grid((unsigned)(assignments < 65536 ? assignments : 65536));
+    FRB_DISPATCH_DTYPE(x_dtype, InT, FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+        launch_dependent(scaled_rows_kernel<InT, OutT>, grid, dim3(128), 0, stream, (const InT*)x, weights, row_of_assign,
+                         (OutT*)out, assignments, top_k, width);
+    }));
+    FRB_RETURN_LAUNCH("scaled_rows");
+}

@@ -48,7 +48,13 @@ class DecoderModel:
                 build_part("feed_forward", layer.feed_forward, self.dtype) if layer.feed_forward is not None else None,
                 build_part("norm", layer.mixer_norm, self.dtype),
                 build_part("norm", layer.feed_forward_norm, self.dtype) if layer.feed_forward_norm is not None else None))
+        self.additions = [build_part("addition", layer.addition, self.dtype) if layer.addition is not None else None
+                          for layer in plan.layers]
         self.connectors = [build_part("connector", spec, self.dtype) for spec in plan.connectors]
+        # an embedding with state of its own (the token before) gets a cache line behind those of the run order
+        self.embedding_line: Optional[int] = None
+        if hasattr(self.embedding, "cache_need") and self.embedding.cache_need().state_shape:
+            self.embedding_line = max((run.cache_line for run in plan.run_order), default=-1) + 1
         self.final_norm = build_part("norm", plan.final_norm, self.dtype)
         self.head = build_part("head", plan.head, self.dtype)
         self.head_is_tied = plan.head.tensors.get("weight") == plan.embedding.tensors.get("weight")
@@ -58,8 +64,10 @@ class DecoderModel:
     def all_parts(self):
         parts = [self.embedding]
         parts.extend(self.connectors)
-        for block in self.blocks:
+        for block, addition in zip(self.blocks, self.additions):
             parts.extend(block.parts())
+            if addition is not None:
+                parts.append(addition)
         parts.append(self.final_norm)
         parts.append(self.head)
         flat = []
@@ -81,9 +89,11 @@ class DecoderModel:
         self.embedding.load(source)
         for connector in self.connectors:
             connector.load(source)
-        for block in self.blocks:
+        for block, addition in zip(self.blocks, self.additions):
             for part in block.parts():
                 part.load(source)
+            if addition is not None:
+                addition.load(source)
         self.final_norm.load(source)
         if self.head_is_tied:
             self.head.load(source, shared=self.embedding.weight)
@@ -124,10 +134,16 @@ class DecoderModel:
             if run.writes_cache:
                 needs[run.cache_line] = need
             elif needs[run.cache_line] != need:
-                raise ValueError(
-                    f"layer {run.layer} reads cache line {run.cache_line}, whose writer needs {needs[run.cache_line]}, "
-                    f"but itself needs {need}")
-        return [n if n is not None else CacheNeed() for n in needs]
+                try:                                   # a reader with a window of its own: the line keeps the wider one
+                    needs[run.cache_line] = needs[run.cache_line].shared_with(need)
+                except ValueError:
+                    raise ValueError(
+                        f"layer {run.layer} reads cache line {run.cache_line}, whose writer needs {needs[run.cache_line]}, "
+                        f"but itself needs {need}") from None
+        needs = [n if n is not None else CacheNeed() for n in needs]
+        if self.embedding_line is not None:
+            needs.append(self.embedding.cache_need())
+        return needs
 
     def new_cache(self, max_tokens: int, num_slots: Optional[int] = None, device="cuda") -> SequenceCache:
         cache = SequenceCache(self.cache_needs(), max_tokens=max_tokens, num_slots=num_slots, dtype=self.dtype,
@@ -141,7 +157,11 @@ class DecoderModel:
                 logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
-        x = self.embedding.forward(ctx, tokens)
+        ctx.step_tokens = tokens                        # parts that take a further input per token read the ids here
+        if self.embedding_line is not None:
+            x = self.embedding.forward(ctx, tokens, cache.line(self.embedding_line))
+        else:
+            x = self.embedding.forward(ctx, tokens)
         first = None
         if self.connectors:
             # a connector mixes the embedding's rows back in; the stream itself is updated in place from here on
@@ -152,6 +172,8 @@ class DecoderModel:
             if run.connector is not None:
                 x, pending = self.connectors[run.connector[0]].forward(ctx, x, pending, first, run.connector[1]), None
             x, pending = self.blocks[run.layer].forward(ctx, x, pending, cache.line(run.cache_line), run.writes_cache)
+            if self.additions[run.layer] is not None:
+                x, pending = self.additions[run.layer].forward(ctx, x, pending)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         act, _ = self.final_norm.forward(ctx, x, delta=pending, rows=logit_rows, write_back=False)

@@ -22,6 +22,8 @@ Interfaces
     the other place of a norm: x <- x + norm(update), for blocks whose sublayers read x itself.
 ``Connector.forward(ctx, x, pending, first, index)`` -> the new stream [T, width] (float32)
     a part between two runs that rewrites the whole stream; ``first`` holds the embedding's rows.
+``Addition.forward(ctx, x, pending)`` -> (x, pending)
+    a part behind a layer's block that adds to the stream once more (a further input per layer and token).
 """
 from __future__ import annotations
 
@@ -193,6 +195,27 @@ class Connector(Part):
         raise NotImplementedError
 
 
+class Addition(Part):
+    """A part behind a layer's block that adds to the stream once more; it may read the step's token ids
+    (``ctx.step_tokens``, on the device).  ``forward(ctx, x, pending)`` gets the stream and the update that the block
+    left unsummed, and returns the two in the same form."""
+
+    def forward(self, ctx, x: torch.Tensor, pending):
+        raise NotImplementedError
+
+
+def shared_fetch(source: TensorSource, need: TensorNeed) -> torch.Tensor:
+    """A tensor that several parts read (one table with a share per layer): fetched once per source and kept with it."""
+    try:
+        kept = source.__dict__.setdefault("_shared_tensors", {})
+    except AttributeError:
+        return source.fetch(need)
+    key = (need.name, need.role)
+    if key not in kept:
+        kept[key] = source.fetch(need)
+    return kept[key]
+
+
 class Block:
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
         self.mixer, self.feed_forward = mixer, feed_forward
@@ -208,7 +231,7 @@ class Block:
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
-    "connector": {},
+    "connector": {}, "addition": {},
 }
 
 

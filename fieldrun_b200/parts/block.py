@@ -17,6 +17,8 @@ class PreNormBlock(Block):
             pending = as_tensor(ctx, pending)
         act, _ = self.mixer_norm.forward(ctx, x, delta=pending)
         update = self.mixer.forward(ctx, act, line, writes_cache)
+        if self.feed_forward is None:                  # a layer without feed-forward: the next norm adds the mixer's update
+            return x, update
         if not self.feed_forward_norm.accepts_deferred:
             update = as_tensor(ctx, update)
         act2, act2_32 = self.feed_forward_norm.forward(ctx, x, delta=update,

@@ -9,6 +9,11 @@ summed with their weights in rank order.  The experts' matrices are stacked:
 ``w13`` [E, 2I, d] holds each expert's gate rows then its up rows, ``w2`` [E, d, I].
 Rows are grouped by expert with a counting sort on the device, so no step of the
 feed-forward waits for the host.
+
+Two more forms, each an argument: ``gate_limit`` > 0 makes an expert's unit the clamped gate g = min(x W1^T, limit),
+u = clamp(x W3^T, -limit, limit), g sigmoid(1.702 g) (u + 1); ``weight_on_input`` puts an expert's weight on what goes
+in instead of on what comes out: the token's output is the sum of expert(w x) over its experts.  The rows are then
+scaled and sorted by a kernel of their own (product in float32, rounded once) and summed with weights of one.
 """
 from __future__ import annotations
 
@@ -56,6 +61,11 @@ class RoutedExperts(FeedForward):
         self.renormalize = (int(bool(a.get("renormalize", True))) | (ops.ROUTE_SOFTMAX if self.score == "softmax" else 0)
                             | (ops.ROUTE_FLOOR if floor else 0))
         self.routed_scale = float(a.get("routed_scale", 1.0))
+        self.gate_limit = float(a.get("gate_limit") or 0.0)
+        if self.gate_limit < 0.0:
+            raise ValueError(f"a gate limit of {self.gate_limit}")
+        self.weight_on_input = bool(a.get("weight_on_input", False))
+        self._ones: Optional[torch.Tensor] = None
         if not 1 <= self.top_k <= self.num_experts:
             raise ValueError(f"top_k {self.top_k} is outside 1..{self.num_experts} experts")
         if not (dtype == torch.bfloat16 and self.hidden_size % 128 == 0 and self.expert_width % 128 == 0):
@@ -158,37 +168,44 @@ class RoutedExperts(FeedForward):
                         p["row_of_assign"], p["tile_expert"], p["tile_row0"], p["num_tiles"])
         return p
 
-    def experts(self, ctx, act: torch.Tensor, p) -> torch.Tensor:
-        """y [N, d] float32: the output of its expert for every (token, rank), in expert-sorted order."""
+    def experts(self, ctx, act: torch.Tensor, p, scaled: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """y [N, d] float32: the output of its expert for every (token, rank), in expert-sorted order.  ``scaled``: the
+        experts' input rows already in that order (each token's row times its expert's weight) instead of ``act``."""
         hidden = ctx.buffer("experts.hidden", (p["rows"], self.expert_width), self.dtype)
         y = ctx.buffer("experts.y", (p["rows"], self.hidden_size), torch.float32)
+        limit = self.gate_limit
+        sorted_token = p["sorted_token"]
+        if scaled is not None:
+            act, sorted_token = scaled, None
         if self.on_tensor_cores(p["rows"], ctx.is_decode):
-            gathered = ctx.buffer("experts.gathered", (p["rows"], self.hidden_size), self.dtype)
-            ops.gather_rows(act, p["sorted_token"], gathered)
+            gathered = scaled
+            if gathered is None:
+                gathered = ctx.buffer("experts.gathered", (p["rows"], self.hidden_size), self.dtype)
+                ops.gather_rows(act, p["sorted_token"], gathered)
             ops.expert_gemm_tc(self.w13, gathered, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
-                               p["max_tiles"], p["tile_rows"], hidden, paired=True)
+                               p["max_tiles"], p["tile_rows"], hidden, paired=True, gate_limit=limit)
             ops.expert_gemm_tc(self.w2, hidden, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                                p["max_tiles"], p["tile_rows"], y, paired=False)
             return y
         if self.streams() and ops.weight_stream_takes(self.expert_width, self.hidden_size, paired=True) \
                 and ops.weight_stream_takes(self.hidden_size, self.expert_width, paired=False):
-            ops.weight_stream(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
-                              p["max_tiles"], p["tile_rows"], hidden, paired=True)
+            ops.weight_stream(self.w13, act, sorted_token, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
+                              p["max_tiles"], p["tile_rows"], hidden, paired=True, gate_limit=limit)
             # the second product's lists are the first one's: its weights may be on their way while the first still runs
             ops.weight_stream(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                               p["max_tiles"], p["tile_rows"], y, paired=False, lists_final=True)
             return y
         if self.streams():
             tiles = min(p["rows"], self.num_experts)           # about as many tiles as experts that got rows
-            ops.expert_gemm_mma(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
-                                p["offsets"], p["max_tiles"], p["tile_rows"], hidden, paired=True,
+            ops.expert_gemm_mma(self.w13, act, sorted_token, p["tile_expert"], p["tile_row0"], p["num_tiles"],
+                                p["offsets"], p["max_tiles"], p["tile_rows"], hidden, paired=True, gate_limit=limit,
                                 **ops.stream_shape(tiles, self.expert_width, self.hidden_size, p["tile_rows"], paired=True))
             ops.expert_gemm_mma(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                                 p["max_tiles"], p["tile_rows"], y, paired=False,
                                 **ops.stream_shape(tiles, self.hidden_size, self.expert_width, p["tile_rows"]))
             return y
-        ops.expert_gemm_generic(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
-                                p["offsets"], p["max_tiles"], hidden, paired=True)
+        ops.expert_gemm_generic(self.w13, act, sorted_token, p["tile_expert"], p["tile_row0"], p["num_tiles"],
+                                p["offsets"], p["max_tiles"], hidden, paired=True, gate_limit=limit)
         ops.expert_gemm_generic(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                                 p["max_tiles"], y, paired=False)
         return y
@@ -242,6 +259,14 @@ class RoutedExperts(FeedForward):
             ids, weights = self.route(ctx, act32)
             self._tell_route(ids)
             p = self.plan(ctx, ids)
+        if self.weight_on_input:
+            # the weight belongs on what goes in: a row per (token, rank), scaled (float32 row times weight, rounded once)
+            scaled = ctx.buffer("experts.scaled", (p["rows"], self.hidden_size), self.dtype)
+            ops.scaled_rows(act32, weights, p["row_of_assign"], scaled)
+            y = self.experts(ctx, act, p, scaled)
+            if self._ones is None or self._ones.shape[0] < weights.shape[0] or self._ones.device != weights.device:
+                self._ones = torch.ones((max(weights.shape[0], 1024), self.top_k), dtype=torch.float32, device=weights.device)
+            return WeightedRows(y, self._ones[:weights.shape[0]], p["row_of_assign"])
         y = self.experts(ctx, act, p)
         # each token's expert outputs, not yet summed: the norm after this layer adds them in rank order
         return WeightedRows(y, weights, p["row_of_assign"])
@@ -299,6 +324,8 @@ class DenseUnit(FeedForward):
         self.activation = str(spec.args["activation"])
         if self.activation not in ops.ACTIVATIONS:
             raise ValueError(f"activation {self.activation!r} is none of {sorted(ops.ACTIVATIONS)}")
+        if not (dtype == torch.bfloat16 and self.width % 128 == 0 and self.hidden_size % 64 == 0):
+            self.kernel_groups = ("common", "streams")         # sizes the tcgen05 product never takes
         self.w_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
         self._tiles: dict = {}
