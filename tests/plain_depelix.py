@@ -64,11 +64,11 @@ def latent_queries(h, w_down, norm, w_up, eps, heads, dim, rot_dim):
     return (latent @ w_up.T).reshape(h.shape[0], heads, dim + rot_dim)
 
 
-def latent_keys(h, w_down, norm, eps, kv_rank, rot_dim, positions, base, interleaved):
+def latent_keys(h, w_down, norm, eps, kv_rank, rot_dim, positions, base, dims, interleaved):
     """(c [T, kv_rank] normed, r [T, rot_dim] rotated): what a layer keeps of its keys and values."""
     both = h @ w_down.T
     latent = rms_norm(both[:, :kv_rank], norm, eps)
-    shared = rotate(both[:, kv_rank:kv_rank + rot_dim], positions, base, rot_dim, interleaved)
+    shared = rotate(both[:, kv_rank:kv_rank + rot_dim], positions, base, dims, interleaved)
     return latent, shared
 
 
@@ -91,13 +91,13 @@ def latent_attention(h, t, prefix, mixer, eps, *, interleaved, window, gate_per_
     None for a layer with a down-projection of its own.  Returns (update [T, width], (c, r))."""
     count = h.shape[0]
     heads, dim, rot_dim, vdim, kv_rank = mixer["heads"], mixer["dim"], mixer["rot_dim"], mixer["vdim"], mixer["kv_rank"]
-    base = mixer["rot"]["base"]
+    base, dims = mixer["rot"]["base"], mixer["rot"]["dims"]
     positions = np.arange(count)
     q = latent_queries(h, t[prefix + "dq"], t[prefix + "dq.norm"], t[prefix + "uq"], eps, heads, dim, rot_dim)
     q_plain = q[:, :, :dim]
-    q_rot = rotate(q[:, :, dim:], positions, base, rot_dim, interleaved)
+    q_rot = rotate(q[:, :, dim:], positions, base, dims, interleaved)
     if kept is None:
-        kept = latent_keys(h, t[prefix + "dkv"], t[prefix + "dkv.norm"], eps, kv_rank, rot_dim, positions, base, interleaved)
+        kept = latent_keys(h, t[prefix + "dkv"], t[prefix + "dkv.norm"], eps, kv_rank, rot_dim, positions, base, dims, interleaved)
     latent, shared = kept
     k_plain = (latent @ t[prefix + "uk"].T).reshape(count, heads, dim)
     values = (latent @ t[prefix + "uv"].T).reshape(count, heads, vdim)
@@ -151,12 +151,24 @@ def token_side(x, tokens, side_table, index, dim, w_gate, w_proj, norm, eps):
     return rms_norm(y, norm, eps)
 
 
+def route_margins(h, w_router, top):
+    """Per token, the gap between the last chosen score and the first one left out (infinite if all are chosen)."""
+    scores = np.sort(sigmoid(h @ w_router.T), axis=-1)[:, ::-1]
+    if top >= scores.shape[1]:
+        return np.full(h.shape[0], np.inf)
+    return scores[:, top - 1] - scores[:, top]
+
+
 def forward(config, t, tokens, forced_routes=None, record=None):
     """Logits [T, vocab] of one sequence from its first token.  ``forced_routes``: {layer: ids [T, top]}.
-    ``record``: a list that gets the stream after every layer; a dict that gets each routed layer's own choice."""
+    ``record``: a list that gets the stream after every layer; a dict that gets each routed layer's own choice and
+    the margins of that choice, {layer: (ids, margins)}."""
     eps = config["norm"]["eps"]
-    pair = config["embedding"]["bigram"]
-    x = embed(tokens, t["embed"], t["bigram"], pair["buckets"], pair["mul_prev"], pair["mul_cur"])
+    pair = (config.get("embedding") or {}).get("bigram")
+    if pair is None:
+        x = t["embed"][np.asarray(tokens)]
+    else:
+        x = embed(tokens, t["embed"], t["bigram"], pair["buckets"], pair["mul_prev"], pair["mul_cur"])
     kept = {}
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
@@ -176,10 +188,11 @@ def forward(config, t, tokens, forced_routes=None, record=None):
             else:
                 update, ids = experts_ff(h, t, p + "mlp.", mlp, None if forced_routes is None else forced_routes.get(i))
                 if isinstance(record, dict):
-                    record[i] = ids
+                    record[i] = (ids, route_margins(h, t[p + "mlp.router"], mlp["router"]["top"]))
                 x = x + update
-        x = x + token_side(x, tokens, t["side.embed"], i, config["token_side"]["dim"], t[p + "side.gate"],
-                           t[p + "side.proj"], t[p + "side.norm"], eps)
+        if config.get("token_side") is not None:
+            x = x + token_side(x, tokens, t["side.embed"], i, config["token_side"]["dim"], t[p + "side.gate"],
+                               t[p + "side.proj"], t[p + "side.norm"], eps)
         if isinstance(record, list):
             record.append(x.copy())
     return rms_norm(x, t["final.norm"], eps) @ t["head"].T
