@@ -13,6 +13,10 @@ the same experts.  It measures
 * every kernel of one prompt step and one decode step, timed alone with CUDA events (``ops.timing_start``), summed
   by kernel name.
 
+``--design depelix``: a Depelix model (attention through latents: every earlier key, a window, a window over the
+layer before's latents, in turn; a hashed pair table on the embedding, a per-layer token input, routed experts with a
+clamped gate fed with weighted inputs) beside a MiniMax-M2 model with as many experts of the same size.
+
 The weights of every model are far larger than the L2 cache, and each timed step reads all of them.
 """
 from __future__ import annotations
@@ -76,6 +80,31 @@ def fotanex_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, 
                          "mask": {"size": FOTANEX_CHUNK}},
                 "right": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}, "mlp": mlp})
     return {"architecture": "Fotanex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": listed}
+
+
+# the Depelix comparison: latents as published models with such attention size them for 128-entry heads
+DEPELIX_EXPERTS, DEPELIX_TOP, DEPELIX_FF_SHARE = 16, 2, 4
+DEPELIX_WINDOW = 1024
+DEPELIX_KV_RANK, DEPELIX_ROT = 512, 64
+
+
+def depelix_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, Any]:
+    """Layers in turns of four: every earlier key, a window, a window over the layer before's latents, every earlier
+    key; all with routed experts, a per-layer token input of 256 entries and a pair table of 65,536 hashed rows."""
+    mlp = {"kind": "moe", "expert": {"ff": ff // DEPELIX_FF_SHARE // 128 * 128, "limit": 7.0},
+           "router": {"experts": DEPELIX_EXPERTS, "top": DEPELIX_TOP}}
+    listed = []
+    for index in range(layers):
+        turn = index % 4
+        mixer = {"heads": heads, "dim": dim, "rot_dim": DEPELIX_ROT, "vdim": dim, "kv_rank": DEPELIX_KV_RANK, "q_rank": 3 * width // 4,
+                 "rot": {"base": 10000.0, "dims": DEPELIX_ROT}, "scale": (dim + DEPELIX_ROT) ** -0.5}
+        if turn in (1, 2):
+            mixer["mask"] = {"size": DEPELIX_WINDOW}
+        if turn == 2:
+            mixer["kv_from"] = index - 1
+        listed.append({"type": "latent_attention" if turn in (1, 2) else "latent_attention_2", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Depelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": 256},
+            "embedding": {"bigram": {"buckets": 65536, "mul_prev": 1000003, "mul_cur": 7919}}, "layers": listed}
 
 
 def minimax_config(width, heads, kv_heads, dim, ff, layers, vocab, experts=None) -> dict[str, Any]:
@@ -171,6 +200,9 @@ def compare_designs(sizes=("w2048", "w4096"), steps: int = 8, warmup: int = 3, d
         if design == "fotanex":
             experts = (FOTANEX_EXPERTS, FOTANEX_TOP, size["ff"] // FOTANEX_FF_SHARE // 128 * 128)
             pair = (("fotanex", fotanex_config(**size)), ("minimax_m2", minimax_config(**size, experts=experts)))
+        elif design == "depelix":
+            experts = (DEPELIX_EXPERTS, DEPELIX_TOP, size["ff"] // DEPELIX_FF_SHARE // 128 * 128)
+            pair = (("depelix", depelix_config(**size)), ("minimax_m2", minimax_config(**size, experts=experts)))
         else:
             pair = (("bamasun", bamasun_config(**size)), ("minimax_m2", minimax_config(**size)))
         for design_name, config in pair:

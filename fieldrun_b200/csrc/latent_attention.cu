@@ -287,3 +287,314 @@ FRB_API int frb_latent_gate(const float* o, const float* gate, int gate_stride, 
     });
     FRB_RETURN_LAUNCH("latent_gate");
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// latent_attention_mma: the same attention on tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 scores,
+// statistics and sums), for prompts and for single tokens.
+//
+// A block of 8 warps takes M = 16 MT rows: TQ neighbouring tokens x M / TQ heads.  All rows of one sequence read the same
+// key rows, so a tile of 32 key rows [c ; r] in shared memory serves every head and every token of the block; the next
+// tile is on its way (cp.async) while this one is used.  Per tile:
+//   scores   warp w takes the 8 keys (w & 3) of the tile and half of the row tiles: S = Q K^T over all D entries;
+//   softmax  the four warps of a row exchange their maxima through shared memory; p = exp2(s - m) goes to shared
+//            memory as bfloat16, the factor for what was summed before beside it;
+//   sums     warp w takes the latent entries 8 (w + 8 n) .. + 7 of all rows: O = O * factor + P C, C being the first R
+//            entries of the same key rows, read transposed (ldmatrix.trans).
+// Tokens of a block that belong to different sequences are taken one sequence after the other.
+// Sizes: R a multiple of 8 up to 512, R + P a multiple of 16.
+#define LM_THREADS 256
+#define LM_KEYS 32
+#define LM_PSTRIDE 40
+
+struct LatentMmaParams {
+    const bf16* q_lat;          // [H, T, R]
+    const bf16* q_rot;          // [T, H, P]
+    const bf16* k_pages;        // [pages, 1, 64, R + P]
+    const int* page_table;
+    const int* tok_pos;
+    const int* tok_slot;
+    bf16* out;                  // [H, T, R]
+    float scale2;               // softmax scale * log2(e)
+    int window, max_pages, num_tokens, num_heads, rank, rot_dim;
+    int tokens_per_block;       // TQ; a block's rows are TQ tokens x (M / TQ) heads
+};
+
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* at) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(at);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lm_ldmatrix_x2(uint32_t& r0, uint32_t& r1, const bf16* at) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(at);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(a));
+}
+__device__ __forceinline__ void lm_ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const bf16* at) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(at);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(a));
+}
+__device__ __forceinline__ void lm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void lm_copy16(bf16* to, const bf16* from) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(to);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(from) : "memory");
+}
+__device__ __forceinline__ void lm_copies_done() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+template <int MT, int NTW>
+__global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(LatentMmaParams p) {
+    after_previous_kernel();
+    constexpr int M = 16 * MT;
+    constexpr int RT_S = MT >= 2 ? MT / 2 : 1;           // row tiles of a warp in the score phase
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    const int R = p.rank, D = p.rank + p.rot_dim, DS = D + 8, chunks = D / 8;
+    bf16* q_s = reinterpret_cast<bf16*>(lm_smem);        // [M][DS]
+    bf16* k_s = q_s + (size_t)M * DS;                    // [2][LM_KEYS][DS]
+    bf16* p_s = k_s + (size_t)2 * LM_KEYS * DS;          // [M][LM_PSTRIDE]
+    float* pmax = reinterpret_cast<float*>(p_s + M * LM_PSTRIDE);     // [4][M]
+    float* corr = pmax + 4 * M;                          // [M]
+    float* lsum = corr + M;                              // [4][M]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+    const int TQ = p.tokens_per_block, HB = M / TQ;
+    const int t0 = blockIdx.x * TQ, h0 = blockIdx.y * HB;
+    const int T = p.num_tokens, H = p.num_heads;
+
+    // the queries of all rows: [a_h ; b_h] per row, zeros for rows without a token or head
+    for (int i = tid; i < M * chunks; i += LM_THREADS) {
+        const int r = i / chunks, c = i - r * chunks;
+        const int tok = t0 + r / HB, head = h0 + r % HB;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (tok < T && head < H) {
+            const int d = c * 8;
+            const bf16* src = d < R ? p.q_lat + ((size_t)head * T + tok) * R + d
+                                    : p.q_rot + ((size_t)tok * H + head) * p.rot_dim + (d - R);
+            v = *reinterpret_cast<const uint4*>(src);
+        }
+        *reinterpret_cast<uint4*>(q_s + (size_t)r * DS + c * 8) = v;
+    }
+
+    const int nt = warp & 3, rg = warp >> 2;
+    const bool scores_here = rg * RT_S < MT;
+
+    int seg = 0;
+    while (seg < TQ && t0 + seg < T) {
+        // the run of tokens of one sequence that starts at token t0 + seg
+        const int slot = p.tok_slot[t0 + seg];
+        int seg_end = seg + 1;
+        while (seg_end < TQ && t0 + seg_end < T && p.tok_slot[t0 + seg_end] == slot) ++seg_end;
+        int lo_min = 0x7fffffff, hi_max = -1;
+        for (int i = seg; i < seg_end; ++i) {
+            const int pos = p.tok_pos[t0 + i];
+            lo_min = min(lo_min, first_visible_key(pos, p.window, 0));
+            hi_max = max(hi_max, pos);
+        }
+        const int* table = p.page_table + (size_t)slot * p.max_pages;
+        const int j_begin = lo_min / LM_KEYS * LM_KEYS;
+        const int tiles = (hi_max - j_begin) / LM_KEYS + 1;
+
+        // rows of this warp in the score phase: row tile rg * RT_S + i, rows g and g + 8 of it
+        int row_lo[RT_S][2], row_hi[RT_S][2];
+        float m_run[RT_S][2], l_run[RT_S][2];
+#pragma unroll
+        for (int i = 0; i < RT_S; ++i)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = (rg * RT_S + i) * 16 + g + 8 * h;
+                const int ti = r / HB, head = h0 + r % HB;
+                const bool valid = scores_here && ti >= seg && ti < seg_end && head < H;
+                const int pos = valid ? p.tok_pos[t0 + ti] : -1;
+                row_hi[i][h] = pos;
+                row_lo[i][h] = valid ? first_visible_key(pos, p.window, 0) : 0;
+                m_run[i][h] = -INFINITY;
+                l_run[i][h] = 0.f;
+            }
+        float o[MT][NTW][4];
+#pragma unroll
+        for (int a = 0; a < MT; ++a)
+#pragma unroll
+            for (int n = 0; n < NTW; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[a][n][e] = 0.f;
+
+        auto fetch_tile = [&](int tile) {
+            const int j0 = j_begin + tile * LM_KEYS;
+            const int page = table[j0 / FRB_PAGE];
+            bf16* dst = k_s + (size_t)(tile & 1) * LM_KEYS * DS;
+            const bf16* src = p.k_pages + ((size_t)(page < 0 ? 0 : page) * FRB_PAGE + j0 % FRB_PAGE) * D;
+            for (int i = tid; i < LM_KEYS * chunks; i += LM_THREADS) {
+                const int key = i / chunks, c = i - key * chunks;
+                if (page >= 0) lm_copy16(dst + (size_t)key * DS + c * 8, src + (size_t)key * D + c * 8);
+                else *reinterpret_cast<uint4*>(dst + (size_t)key * DS + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        };
+
+        fetch_tile(0);
+        for (int tile = 0; tile < tiles; ++tile) {
+            lm_copies_done();
+            __syncthreads();                             // the tile is here; everyone is done with the tile before
+            if (tile + 1 < tiles) fetch_tile(tile + 1);
+            const bf16* kb = k_s + (size_t)(tile & 1) * LM_KEYS * DS;
+            const int j0 = j_begin + tile * LM_KEYS;
+
+            float s[RT_S][4];
+            if (scores_here) {
+#pragma unroll
+                for (int i = 0; i < RT_S; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+                const bf16* k_at = kb + (size_t)(nt * 8 + (lane & 7)) * DS + ((lane >> 3) & 1) * 8;
+                const bf16* q_at = q_s + (size_t)(rg * RT_S * 16 + (lane & 15)) * DS + (lane >> 4) * 8;
+                for (int k0 = 0; k0 < D; k0 += 16) {
+                    uint32_t b0, b1;
+                    lm_ldmatrix_x2(b0, b1, k_at + k0);
+#pragma unroll
+                    for (int i = 0; i < RT_S; ++i) {
+                        uint32_t a0, a1, a2, a3;
+                        lm_ldmatrix_x4(a0, a1, a2, a3, q_at + (size_t)i * 16 * DS + k0);
+                        lm_mma(s[i], a0, a1, a2, a3, b0, b1);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < RT_S; ++i)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float mx = -INFINITY;
+#pragma unroll
+                        for (int d = 0; d < 2; ++d) {
+                            const int j = j0 + nt * 8 + 2 * tq + d;
+                            const bool seen = j >= row_lo[i][h] && j <= row_hi[i][h];
+                            const float v = seen ? s[i][2 * h + d] * p.scale2 : -INFINITY;
+                            s[i][2 * h + d] = v;
+                            mx = fmaxf(mx, v);
+                        }
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                        if (tq == 0) pmax[nt * M + (rg * RT_S + i) * 16 + g + 8 * h] = mx;
+                    }
+            }
+            __syncthreads();
+            if (scores_here) {
+#pragma unroll
+                for (int i = 0; i < RT_S; ++i)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int r = (rg * RT_S + i) * 16 + g + 8 * h;
+                        const float m_new = fmaxf(fmaxf(m_run[i][h], fmaxf(pmax[r], pmax[M + r])), fmaxf(pmax[2 * M + r], pmax[3 * M + r]));
+                        const float factor = m_new == -INFINITY ? 1.f : exp2f(m_run[i][h] - m_new);
+                        const float p0 = s[i][2 * h] == -INFINITY ? 0.f : exp2f(s[i][2 * h] - m_new);
+                        const float p1 = s[i][2 * h + 1] == -INFINITY ? 0.f : exp2f(s[i][2 * h + 1] - m_new);
+                        l_run[i][h] = l_run[i][h] * factor + p0 + p1;
+                        m_run[i][h] = m_new;
+                        *reinterpret_cast<__nv_bfloat162*>(p_s + r * LM_PSTRIDE + nt * 8 + 2 * tq) = __floats2bfloat162_rn(p0, p1);
+                        if (nt == 0 && tq == 0) corr[r] = factor;
+                    }
+            }
+            __syncthreads();
+            // sums: O = O * factor + P C for this warp's latent entries
+#pragma unroll
+            for (int a = 0; a < MT; ++a) {
+                const float f0 = corr[a * 16 + g], f1 = corr[a * 16 + g + 8];
+#pragma unroll
+                for (int n = 0; n < NTW; ++n) { o[a][n][0] *= f0; o[a][n][1] *= f0; o[a][n][2] *= f1; o[a][n][3] *= f1; }
+            }
+#pragma unroll
+            for (int kk = 0; kk < LM_KEYS; kk += 16) {
+                uint32_t pa[MT][4];
+#pragma unroll
+                for (int a = 0; a < MT; ++a)
+                    lm_ldmatrix_x4(pa[a][0], pa[a][1], pa[a][2], pa[a][3], p_s + (a * 16 + (lane & 15)) * LM_PSTRIDE + kk + (lane >> 4) * 8);
+#pragma unroll
+                for (int n = 0; n < NTW; ++n) {
+                    const int d0 = (warp + 8 * n) * 8;
+                    if (d0 < R) {
+                        uint32_t b0, b1;
+                        lm_ldmatrix_x2_trans(b0, b1, kb + (size_t)(kk + (lane & 15)) * DS + d0);
+#pragma unroll
+                        for (int a = 0; a < MT; ++a) lm_mma(o[a][n], pa[a][0], pa[a][1], pa[a][2], pa[a][3], b0, b1);
+                    }
+                }
+            }
+        }
+        // the rows' sums of weights, then the output of this run's rows
+        if (scores_here) {
+#pragma unroll
+            for (int i = 0; i < RT_S; ++i)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float l = l_run[i][h];
+                    l += __shfl_xor_sync(0xffffffffu, l, 1);
+                    l += __shfl_xor_sync(0xffffffffu, l, 2);
+                    if (tq == 0) lsum[nt * M + (rg * RT_S + i) * 16 + g + 8 * h] = l;
+                }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int a = 0; a < MT; ++a)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = a * 16 + g + 8 * h;
+                const int ti = r / HB, head = h0 + r % HB;
+                if (ti < seg || ti >= seg_end || head >= H) continue;
+                const float l = lsum[r] + lsum[M + r] + lsum[2 * M + r] + lsum[3 * M + r];
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                bf16* dst = p.out + ((size_t)head * T + t0 + ti) * R;
+#pragma unroll
+                for (int n = 0; n < NTW; ++n) {
+                    const int d0 = (warp + 8 * n) * 8;
+                    if (d0 < R)
+                        *reinterpret_cast<__nv_bfloat162*>(dst + d0 + 2 * tq) = __floats2bfloat162_rn(o[a][n][2 * h] * inv, o[a][n][2 * h + 1] * inv);
+                }
+            }
+        __syncthreads();                                 // the next run writes the same shared tables
+        seg = seg_end;
+    }
+}
+
+FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const void* k_pages, const int* page_table,
+                                     int max_pages, const int* tok_pos, const int* tok_slot, void* out, int num_tokens,
+                                     int num_heads, int rank, int rot_dim, float scale, int window, int single_tokens,
+                                     cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    FRB_CHECK_ARG(rank >= 8 && rank <= 512 && rank % 8 == 0 && (rank + rot_dim) % 16 == 0 && rot_dim >= 0,
+                  "latent attention on tensor cores: a latent of %d and a key part of %d entries", rank, rot_dim);
+    int padded_heads = 1;
+    while (padded_heads < num_heads && padded_heads < 64) padded_heads *= 2;
+    int rows, per_block;
+    if (single_tokens) {                                 // every token is another sequence: a block per token
+        rows = padded_heads <= 16 ? 16 : padded_heads;
+        per_block = 1;
+    } else {
+        rows = 64;
+        while (rows > 16 && (long long)num_tokens * padded_heads <= rows / 2) rows /= 2;
+        if (padded_heads > rows) padded_heads = rows;
+        per_block = rows / padded_heads;
+    }
+    const int heads_per_block = rows / per_block;
+    LatentMmaParams p;
+    p.q_lat = (const bf16*)q_lat; p.q_rot = (const bf16*)q_rot; p.k_pages = (const bf16*)k_pages; p.page_table = page_table;
+    p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.out = (bf16*)out; p.scale2 = scale * 1.4426950408889634f; p.window = window;
+    p.max_pages = max_pages; p.num_tokens = num_tokens; p.num_heads = num_heads; p.rank = rank; p.rot_dim = rot_dim;
+    p.tokens_per_block = per_block;
+    const int DS = rank + rot_dim + 8;
+    const size_t smem = ((size_t)rows * DS + (size_t)2 * LM_KEYS * DS + (size_t)rows * LM_PSTRIDE) * sizeof(bf16) + (size_t)9 * rows * sizeof(float);
+    dim3 grid((num_tokens + per_block - 1) / per_block, (num_heads + heads_per_block - 1) / heads_per_block);
+#define FRB_LATENT_MMA(MT, NTW)                                                                                        \
+    do {                                                                                                               \
+        auto kernel = latent_attention_mma_kernel<MT, NTW>;                                                            \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        launch_dependent(kernel, grid, dim3(LM_THREADS), smem, stream, p);                                             \
+    } while (0)
+#define FRB_LATENT_MMA_ROWS(MT)                                                                                        \
+    do {                                                                                                               \
+        if (rank <= 64) FRB_LATENT_MMA(MT, 1);                                                                         \
+        else if (rank <= 128) FRB_LATENT_MMA(MT, 2);                                                                   \
+        else if (rank <= 256) FRB_LATENT_MMA(MT, 4);                                                                   \
+        else FRB_LATENT_MMA(MT, 8);                                                                                    \
+    } while (0)
+    if (rows == 16) FRB_LATENT_MMA_ROWS(1);
+    else if (rows == 32) FRB_LATENT_MMA_ROWS(2);
+    else FRB_LATENT_MMA_ROWS(4);
+    FRB_RETURN_LAUNCH("latent_attention_mma");
+}

@@ -69,6 +69,7 @@ _SIGNATURES = {
     "frb_latent_queries": "pppippipiiiiii",
     "frb_latent_attention": "pppipipppiiiifi",
     "frb_latent_gate": "ppiiipiiii",
+    "frb_latent_attention_mma": "ppppipppiiiifii",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -83,7 +84,8 @@ _ENTRY_GROUPS = {
                "frb_unary_unit", "frb_softcap", "frb_gated_unit", "frb_sample_rows", "frb_argmax_rows", "frb_sample_floor",
                "frb_dyt_norm", "frb_rms_blend", "frb_concat_rows", "frb_add_row_vector", "frb_head_gate", "frb_embed_pair_rows",
                "frb_token_side_gate", "frb_add_rms_normed", "frb_add_typed_copy"),
-    "latent": ("frb_latent_prepare", "frb_latent_queries", "frb_latent_attention", "frb_latent_gate"),
+    "latent": ("frb_latent_prepare", "frb_latent_queries", "frb_latent_attention", "frb_latent_gate",
+               "frb_latent_attention_mma"),
     "attention": ("frb_attention_decode_mma", "frb_attention_prefill_mma", "frb_attention_decode_tma", "frb_attention_prefill_tc"),
     "streams": ("frb_weight_stream", "frb_expert_gemm_mma"),
     "experts": ("frb_router_topk", "frb_expert_plan", "frb_expert_combine", "frb_expert_gemm_generic", "frb_route_plan_small",
@@ -1139,6 +1141,26 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Te
     _call("frb_latent_attention", _ptr(q_lat), _ptr(q_rot), _ptr(k_pages), _code(q_lat.dtype), _ptr(page_table),
           page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q_rot.shape[0], num_heads, rank, rot_dim,
           float(scale), int(window or 0))
+
+
+def latent_mma_takes(rank: int, rot_dim: int) -> bool:
+    """Whether the tensor-core kernel takes key rows of ``rank`` + ``rot_dim`` entries (bfloat16 only)."""
+    return 8 <= rank <= 512 and rank % 8 == 0 and (rank + rot_dim) % 16 == 0
+
+
+def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Tensor, page_table: torch.Tensor,
+                         tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int, rank: int,
+                         rot_dim: int, scale: float, window: Optional[int], single_tokens: bool = False) -> None:
+    """``latent_attention`` on tensor cores, bfloat16: blocks of up to 64 (token, head) rows over shared tiles of key
+    rows.  A sequence's tokens lie together, in rising positions.  ``single_tokens``: every token is another sequence
+    (a block per token instead of a block per run of tokens)."""
+    if not (q_lat.dtype == q_rot.dtype == k_pages.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("the tensor-core latent attention takes bfloat16 queries, cache and output")
+    if not latent_mma_takes(rank, rot_dim):
+        raise KernelError(f"the tensor-core latent attention does not take key rows of {rank} + {rot_dim} entries")
+    _call("frb_latent_attention_mma", _ptr(q_lat), _ptr(q_rot), _ptr(k_pages), _ptr(page_table), page_table.shape[1],
+          _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q_rot.shape[0], num_heads, rank, rot_dim, float(scale), int(window or 0),
+          int(single_tokens))
 
 
 def latent_gate(o: torch.Tensor, gate: torch.Tensor, gate_column: int, per_head: bool, out: torch.Tensor, *, heads: int,

@@ -16,7 +16,7 @@ the rotated parts, in halves or neighbouring pairs), ``gate`` ("head": head h's 
 row of W_g per head; "element": the concatenated heads times sigmoid(W_g x) entry by entry; None), ``shares_kv`` (the
 layer has no W_dkv: it attends, with its own queries, U, V, window and gate, over the latents in another layer's cache
 line, which the plan's run order names).  Scores, softmax, both norms and the rotation are float32; the products take
-bfloat16 operands in bfloat16 mode.
+bfloat16 operands in bfloat16 mode (the weights of the softmax too, as operands of the sum over the keys).
 """
 from __future__ import annotations
 
@@ -164,6 +164,13 @@ class LatentAttention(Mixer):
         return linear(out, self.w_o)
 
     def attend(self, ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, line: LineView, o_lat: torch.Tensor) -> None:
+        """bfloat16 and key rows the tensor-core kernel takes: that kernel, for prompts and single tokens alike; the
+        general kernel (float32 arithmetic, any sizes) otherwise."""
+        if self.dtype == torch.bfloat16 and ops.latent_mma_takes(self.kv_rank, self.rot_dim):
+            ops.latent_attention_mma(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
+                                     num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim,
+                                     scale=self.softmax_scale, window=self.window, single_tokens=ctx.is_decode)
+            return
         ops.latent_attention(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
                              num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim, scale=self.softmax_scale,
                              window=self.window)

@@ -52,7 +52,7 @@ CONFIG_A = {
         causal(moe(4, 4, 24, 0.4), 4, 12, 6, 10, 18, 44, 30000.0, 0.22, rot_dims=4),
     ],
 }
-INIT_A = RandomInit(seed=23, matrix_std=0.1, norm_std=0.2, bias_std=0.4)
+INIT_A = RandomInit(seed=23, matrix_std=0.07, norm_std=0.2, bias_std=0.4)
 
 CONFIG_B = {
     "architecture": "Depelix", "vocab": 77, "width": 40, "norm": {"eps": 1e-6},
@@ -63,7 +63,7 @@ CONFIG_B = {
         windowed(None, 2, 12, 4, 16, 20, 16, 2000.0, 0.25, window=64),
     ],
 }
-INIT_B = RandomInit(seed=24, matrix_std=0.16, norm_std=0.1, bias_std=0.5)
+INIT_B = RandomInit(seed=24, matrix_std=0.09, norm_std=0.1, bias_std=0.5)
 
 CONFIG_C = {
     "architecture": "Depelix", "vocab": 200, "width": 128, "norm": {"eps": 1e-6},
