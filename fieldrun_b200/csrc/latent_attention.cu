@@ -292,17 +292,21 @@ FRB_API int frb_latent_gate(const float* o, const float* gate, int gate_stride, 
 // latent_attention_mma: the same attention on tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 scores,
 // statistics and sums), for prompts and for single tokens.
 //
-// A block of 8 warps takes M = 16 MT rows: TQ neighbouring tokens x M / TQ heads.  All rows of one sequence read the same
+// A block of 16 warps takes M = 16 MT rows: TQ neighbouring tokens x M / TQ heads.  All rows of one sequence read the same
 // key rows, so a tile of 32 key rows [c ; r] in shared memory serves every head and every token of the block; the next
 // tile is on its way (cp.async) while this one is used.  Per tile:
-//   scores   warp w takes the 8 keys (w & 3) of the tile and half of the row tiles: S = Q K^T over all D entries;
+//   scores   warp w takes the 8 keys (w & 3) of the tile and a quarter of the row tiles: S = Q K^T over all D entries,
+//            two steps of 16 entries at a time (their loads first, two sums a row tile);
 //   softmax  the four warps of a row exchange their maxima through shared memory; p = exp2(s - m) goes to shared
 //            memory as bfloat16, the factor for what was summed before beside it;
-//   sums     warp w takes the latent entries 8 (w + 8 n) .. + 7 of all rows: O = O * factor + P C, C being the first R
+//   sums     warp w takes the latent entries 8 (w + 16 n) .. + 7 of all rows: O = O * factor + P C, C being the first R
 //            entries of the same key rows, read transposed (ldmatrix.trans).
 // Tokens of a block that belong to different sequences are taken one sequence after the other.
+// Single tokens over long contexts: the keys are cut at fixed multiples of `chunk_keys`, a block per (token, chunk), and
+// latent_combine_kernel joins the chunks' parts in their order.  Where the cuts lie depends on nothing but the
+// positions, so a token's result is the same bit for bit whatever else the step holds.
 // Sizes: R a multiple of 8 up to 512, R + P a multiple of 16.
-#define LM_THREADS 256
+#define LM_THREADS 512
 #define LM_KEYS 32
 #define LM_PSTRIDE 40
 
@@ -317,6 +321,9 @@ struct LatentMmaParams {
     float scale2;               // softmax scale * log2(e)
     int window, max_pages, num_tokens, num_heads, rank, rot_dim;
     int tokens_per_block;       // TQ; a block's rows are TQ tokens x (M / TQ) heads
+    int chunk_keys;             // > 0 (single tokens only): block z takes the keys [z, z + 1) * chunk_keys and leaves its
+    float* part_o;              // unnormalised sums [Z, H, T, R] and
+    float* part_ml;             // (maximum, sum of weights) [Z, H, T, 2] for latent_combine_kernel
 };
 
 __device__ __forceinline__ void lm_ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* at) {
@@ -345,7 +352,7 @@ template <int MT, int NTW>
 __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(LatentMmaParams p) {
     after_previous_kernel();
     constexpr int M = 16 * MT;
-    constexpr int RT_S = MT >= 2 ? MT / 2 : 1;           // row tiles of a warp in the score phase
+    constexpr int RT_S = MT >= 4 ? MT / 4 : 1;           // row tiles of a warp in the score phase
     extern __shared__ __align__(16) unsigned char lm_smem[];
     const int R = p.rank, D = p.rank + p.rot_dim, DS = D + 8, chunks = D / 8;
     bf16* q_s = reinterpret_cast<bf16*>(lm_smem);        // [M][DS]
@@ -354,6 +361,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
     float* pmax = reinterpret_cast<float*>(p_s + M * LM_PSTRIDE);     // [4][M]
     float* corr = pmax + 4 * M;                          // [M]
     float* lsum = corr + M;                              // [4][M]
+    float* mfin = lsum + 4 * M;                          // [M]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
     const int TQ = p.tokens_per_block, HB = M / TQ;
@@ -390,8 +398,13 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
             hi_max = max(hi_max, pos);
         }
         const int* table = p.page_table + (size_t)slot * p.max_pages;
-        const int j_begin = lo_min / LM_KEYS * LM_KEYS;
-        const int tiles = (hi_max - j_begin) / LM_KEYS + 1;
+        int j_begin = lo_min / LM_KEYS * LM_KEYS, j_last = hi_max;
+        if (p.chunk_keys > 0) {
+            j_begin = max(j_begin, (int)blockIdx.z * p.chunk_keys);
+            j_last = min(j_last, ((int)blockIdx.z + 1) * p.chunk_keys - 1);
+        }
+        if (j_last < j_begin) { seg = seg_end; continue; }   // no key of this chunk is visible (the same for every thread)
+        const int tiles = (j_last - j_begin) / LM_KEYS + 1;
 
         // rows of this warp in the score phase: row tile rg * RT_S + i, rows g and g + 8 of it
         int row_lo[RT_S][2], row_hi[RT_S][2];
@@ -440,15 +453,31 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
 
             float s[RT_S][4];
             if (scores_here) {
+                float s_odd[RT_S][4];                    // every second step of 16 entries sums here: two chains a row tile
 #pragma unroll
                 for (int i = 0; i < RT_S; ++i)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
-                const bf16* k_at = kb + (size_t)(nt * 8 + (lane & 7)) * DS + ((lane >> 3) & 1) * 8;
+                    for (int e = 0; e < 4; ++e) s[i][e] = s_odd[i][e] = 0.f;
+                const bf16* k_at = kb + (size_t)(nt * 8 + (lane & 7)) * DS + (lane >> 3) * 8;
                 const bf16* q_at = q_s + (size_t)(rg * RT_S * 16 + (lane & 15)) * DS + (lane >> 4) * 8;
-                for (int k0 = 0; k0 < D; k0 += 16) {
+                int k0 = 0;
+                for (; k0 + 32 <= D; k0 += 32) {         // all loads of two steps, then their products
+                    uint32_t b0, b1, b2, b3, a[RT_S][8];
+                    lm_ldmatrix_x4(b0, b1, b2, b3, k_at + k0);
+#pragma unroll
+                    for (int i = 0; i < RT_S; ++i) {
+                        lm_ldmatrix_x4(a[i][0], a[i][1], a[i][2], a[i][3], q_at + (size_t)i * 16 * DS + k0);
+                        lm_ldmatrix_x4(a[i][4], a[i][5], a[i][6], a[i][7], q_at + (size_t)i * 16 * DS + k0 + 16);
+                    }
+#pragma unroll
+                    for (int i = 0; i < RT_S; ++i) {
+                        lm_mma(s[i], a[i][0], a[i][1], a[i][2], a[i][3], b0, b1);
+                        lm_mma(s_odd[i], a[i][4], a[i][5], a[i][6], a[i][7], b2, b3);
+                    }
+                }
+                if (k0 < D) {                            // D = 16 (2 n + 1): one step is left
                     uint32_t b0, b1;
-                    lm_ldmatrix_x2(b0, b1, k_at + k0);
+                    lm_ldmatrix_x2(b0, b1, kb + (size_t)(nt * 8 + (lane & 7)) * DS + ((lane >> 3) & 1) * 8 + k0);
 #pragma unroll
                     for (int i = 0; i < RT_S; ++i) {
                         uint32_t a0, a1, a2, a3;
@@ -456,6 +485,10 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
                         lm_mma(s[i], a0, a1, a2, a3, b0, b1);
                     }
                 }
+#pragma unroll
+                for (int i = 0; i < RT_S; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[i][e] += s_odd[i][e];
 #pragma unroll
                 for (int i = 0; i < RT_S; ++i)
 #pragma unroll
@@ -505,14 +538,18 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
 #pragma unroll
                 for (int a = 0; a < MT; ++a)
                     lm_ldmatrix_x4(pa[a][0], pa[a][1], pa[a][2], pa[a][3], p_s + (a * 16 + (lane & 15)) * LM_PSTRIDE + kk + (lane >> 4) * 8);
+                uint32_t pb[NTW][2];
 #pragma unroll
                 for (int n = 0; n < NTW; ++n) {
-                    const int d0 = (warp + 8 * n) * 8;
-                    if (d0 < R) {
-                        uint32_t b0, b1;
-                        lm_ldmatrix_x2_trans(b0, b1, kb + (size_t)(kk + (lane & 15)) * DS + d0);
+                    const int d0 = (warp + LM_THREADS / 32 * n) * 8;
+                    if (d0 < R) lm_ldmatrix_x2_trans(pb[n][0], pb[n][1], kb + (size_t)(kk + (lane & 15)) * DS + d0);
+                }
 #pragma unroll
-                        for (int a = 0; a < MT; ++a) lm_mma(o[a][n], pa[a][0], pa[a][1], pa[a][2], pa[a][3], b0, b1);
+                for (int n = 0; n < NTW; ++n) {
+                    const int d0 = (warp + LM_THREADS / 32 * n) * 8;
+                    if (d0 < R) {
+#pragma unroll
+                        for (int a = 0; a < MT; ++a) lm_mma(o[a][n], pa[a][0], pa[a][1], pa[a][2], pa[a][3], pb[n][0], pb[n][1]);
                     }
                 }
             }
@@ -527,6 +564,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
                     l += __shfl_xor_sync(0xffffffffu, l, 1);
                     l += __shfl_xor_sync(0xffffffffu, l, 2);
                     if (tq == 0) lsum[nt * M + (rg * RT_S + i) * 16 + g + 8 * h] = l;
+                    if (tq == 0 && nt == 0) mfin[(rg * RT_S + i) * 16 + g + 8 * h] = m_run[i][h];
                 }
         }
         __syncthreads();
@@ -538,11 +576,21 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
                 const int ti = r / HB, head = h0 + r % HB;
                 if (ti < seg || ti >= seg_end || head >= H) continue;
                 const float l = lsum[r] + lsum[M + r] + lsum[2 * M + r] + lsum[3 * M + r];
+                if (p.chunk_keys > 0) {
+                    const size_t row = ((size_t)blockIdx.z * H + head) * T + t0 + ti;
+                    if (warp == 0 && tq == 0) { p.part_ml[2 * row] = mfin[r]; p.part_ml[2 * row + 1] = l; }
+#pragma unroll
+                    for (int n = 0; n < NTW; ++n) {
+                        const int d0 = (warp + LM_THREADS / 32 * n) * 8;
+                        if (d0 < R) *reinterpret_cast<float2*>(p.part_o + row * R + d0 + 2 * tq) = make_float2(o[a][n][2 * h], o[a][n][2 * h + 1]);
+                    }
+                    continue;
+                }
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
                 bf16* dst = p.out + ((size_t)head * T + t0 + ti) * R;
 #pragma unroll
                 for (int n = 0; n < NTW; ++n) {
-                    const int d0 = (warp + 8 * n) * 8;
+                    const int d0 = (warp + LM_THREADS / 32 * n) * 8;
                     if (d0 < R)
                         *reinterpret_cast<__nv_bfloat162*>(dst + d0 + 2 * tq) = __floats2bfloat162_rn(o[a][n][2 * h] * inv, o[a][n][2 * h + 1] * inv);
                 }
@@ -552,10 +600,34 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
     }
 }
 
+// out[h][t][:] = sum_z 2^(m_z - m) o_z / sum_z 2^(m_z - m) l_z over the chunks that hold visible keys of token t
+__global__ void __launch_bounds__(128) latent_combine_kernel(LatentMmaParams p) {
+    after_previous_kernel();
+    const int t = blockIdx.x, head = blockIdx.y, T = p.num_tokens, H = p.num_heads, R = p.rank;
+    const int pos = p.tok_pos[t];
+    const int z_lo = first_visible_key(pos, p.window, 0) / LM_KEYS * LM_KEYS / p.chunk_keys, z_hi = pos / p.chunk_keys;
+    float m = -INFINITY;
+    for (int z = z_lo; z <= z_hi; ++z) m = fmaxf(m, p.part_ml[2 * (((size_t)z * H + head) * T + t)]);
+    float total = 0.f;
+    for (int z = z_lo; z <= z_hi; ++z) {
+        const float* ml = p.part_ml + 2 * (((size_t)z * H + head) * T + t);
+        if (ml[1] > 0.f) total += exp2f(ml[0] - m) * ml[1];
+    }
+    const float inv = total > 0.f ? 1.0f / total : 0.f;
+    for (int d = threadIdx.x; d < R; d += blockDim.x) {
+        float acc = 0.f;
+        for (int z = z_lo; z <= z_hi; ++z) {
+            const size_t row = ((size_t)z * H + head) * T + t;
+            if (p.part_ml[2 * row + 1] > 0.f) acc += exp2f(p.part_ml[2 * row] - m) * p.part_o[row * R + d];
+        }
+        p.out[((size_t)head * T + t) * R + d] = __float2bfloat16(acc * inv);
+    }
+}
+
 FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const void* k_pages, const int* page_table,
                                      int max_pages, const int* tok_pos, const int* tok_slot, void* out, int num_tokens,
                                      int num_heads, int rank, int rot_dim, float scale, int window, int single_tokens,
-                                     cudaStream_t stream) {
+                                     int chunk_keys, int num_chunks, void* part_o, void* part_ml, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
     FRB_CHECK_ARG(rank >= 8 && rank <= 512 && rank % 8 == 0 && (rank + rot_dim) % 16 == 0 && rot_dim >= 0,
                   "latent attention on tensor cores: a latent of %d and a key part of %d entries", rank, rot_dim);
@@ -577,9 +649,13 @@ FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const
     p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.out = (bf16*)out; p.scale2 = scale * 1.4426950408889634f; p.window = window;
     p.max_pages = max_pages; p.num_tokens = num_tokens; p.num_heads = num_heads; p.rank = rank; p.rot_dim = rot_dim;
     p.tokens_per_block = per_block;
+    FRB_CHECK_ARG(chunk_keys == 0 || (single_tokens && chunk_keys % LM_KEYS == 0 && num_chunks >= 1 && part_o && part_ml),
+                  "latent attention in chunks of %d keys (%d of them): single tokens, a multiple of %d, and room for the parts",
+                  chunk_keys, num_chunks, LM_KEYS);
+    p.chunk_keys = chunk_keys; p.part_o = (float*)part_o; p.part_ml = (float*)part_ml;
     const int DS = rank + rot_dim + 8;
-    const size_t smem = ((size_t)rows * DS + (size_t)2 * LM_KEYS * DS + (size_t)rows * LM_PSTRIDE) * sizeof(bf16) + (size_t)9 * rows * sizeof(float);
-    dim3 grid((num_tokens + per_block - 1) / per_block, (num_heads + heads_per_block - 1) / heads_per_block);
+    const size_t smem = ((size_t)rows * DS + (size_t)2 * LM_KEYS * DS + (size_t)rows * LM_PSTRIDE) * sizeof(bf16) + (size_t)10 * rows * sizeof(float);
+    dim3 grid((num_tokens + per_block - 1) / per_block, (num_heads + heads_per_block - 1) / heads_per_block, chunk_keys > 0 ? num_chunks : 1);
 #define FRB_LATENT_MMA(MT, NTW)                                                                                        \
     do {                                                                                                               \
         auto kernel = latent_attention_mma_kernel<MT, NTW>;                                                            \
@@ -588,13 +664,13 @@ FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const
     } while (0)
 #define FRB_LATENT_MMA_ROWS(MT)                                                                                        \
     do {                                                                                                               \
-        if (rank <= 64) FRB_LATENT_MMA(MT, 1);                                                                         \
-        else if (rank <= 128) FRB_LATENT_MMA(MT, 2);                                                                   \
-        else if (rank <= 256) FRB_LATENT_MMA(MT, 4);                                                                   \
-        else FRB_LATENT_MMA(MT, 8);                                                                                    \
+        if (rank <= 128) FRB_LATENT_MMA(MT, 1);                                                                        \
+        else if (rank <= 256) FRB_LATENT_MMA(MT, 2);                                                                   \
+        else FRB_LATENT_MMA(MT, 4);                                                                                    \
     } while (0)
     if (rows == 16) FRB_LATENT_MMA_ROWS(1);
     else if (rows == 32) FRB_LATENT_MMA_ROWS(2);
     else FRB_LATENT_MMA_ROWS(4);
+    if (chunk_keys > 0) launch_dependent(latent_combine_kernel, dim3(num_tokens, num_heads), dim3(128), 0, stream, p);
     FRB_RETURN_LAUNCH("latent_attention_mma");
 }

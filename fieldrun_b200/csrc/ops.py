@@ -69,7 +69,7 @@ _SIGNATURES = {
     "frb_latent_queries": "pppippipiiiiii",
     "frb_latent_attention": "pppipipppiiiifi",
     "frb_latent_gate": "ppiiipiiii",
-    "frb_latent_attention_mma": "ppppipppiiiifii",
+    "frb_latent_attention_mma": "ppppipppiiiifiiiipp",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -1143,6 +1143,15 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Te
           float(scale), int(window or 0))
 
 
+def latent_key_chunks(max_pages: int) -> tuple[int, int]:
+    """(keys a chunk, chunks) for single tokens over a line of ``max_pages`` pages: chunks of 256 keys, larger ones where
+    the line is so long that there would be more than 32.  It depends on the line's size only, never on a step."""
+    keys = 256
+    while keys * 32 < max_pages * 64:
+        keys *= 2
+    return keys, max(1, -(-max_pages * 64 // keys))
+
+
 def latent_mma_takes(rank: int, rot_dim: int) -> bool:
     """Whether the tensor-core kernel takes key rows of ``rank`` + ``rot_dim`` entries (bfloat16 only)."""
     return 8 <= rank <= 512 and rank % 8 == 0 and (rank + rot_dim) % 16 == 0
@@ -1150,17 +1159,33 @@ def latent_mma_takes(rank: int, rot_dim: int) -> bool:
 
 def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Tensor, page_table: torch.Tensor,
                          tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int, rank: int,
-                         rot_dim: int, scale: float, window: Optional[int], single_tokens: bool = False) -> None:
+                         rot_dim: int, scale: float, window: Optional[int], single_tokens: bool = False,
+                         chunk_keys: int = 0, part_o: Optional[torch.Tensor] = None,
+                         part_ml: Optional[torch.Tensor] = None) -> None:
     """``latent_attention`` on tensor cores, bfloat16: blocks of up to 64 (token, head) rows over shared tiles of key
     rows.  A sequence's tokens lie together, in rising positions.  ``single_tokens``: every token is another sequence
-    (a block per token instead of a block per run of tokens)."""
+    (a block per token instead of a block per run of tokens); with ``chunk_keys`` > 0 a block per (token, chunk of that
+    many keys, cut at fixed multiples), the chunks' sums in ``part_o`` [chunks, heads, T, rank] and their (maximum, sum
+    of weights) in ``part_ml`` [chunks, heads, T, 2], both float32, joined by a second kernel."""
     if not (q_lat.dtype == q_rot.dtype == k_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("the tensor-core latent attention takes bfloat16 queries, cache and output")
     if not latent_mma_takes(rank, rot_dim):
         raise KernelError(f"the tensor-core latent attention does not take key rows of {rank} + {rot_dim} entries")
+    tokens, chunks = q_rot.shape[0], 0
+    if chunk_keys:
+        if not single_tokens or part_o is None or part_ml is None:
+            raise KernelError("latent attention in chunks of keys: single tokens only, and it needs room for the parts")
+        _want(part_o, torch.float32, "the chunks' sums")
+        _want(part_ml, torch.float32, "the chunks' maxima and sums of weights")
+        chunks = part_o.shape[0]
+        if chunks * chunk_keys < page_table.shape[1] * 64:         # a page holds 64 keys (FRB_PAGE)
+            raise KernelError(f"{chunks} chunks of {chunk_keys} keys do not cover {page_table.shape[1]} pages")
+        if tuple(part_o.shape) != (chunks, num_heads, tokens, rank) or tuple(part_ml.shape) != (chunks, num_heads, tokens, 2):
+            raise KernelError(f"parts of shapes {tuple(part_o.shape)} and {tuple(part_ml.shape)} for {chunks} chunks, "
+                              f"{num_heads} heads, {tokens} tokens and a latent of {rank}")
     _call("frb_latent_attention_mma", _ptr(q_lat), _ptr(q_rot), _ptr(k_pages), _ptr(page_table), page_table.shape[1],
-          _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q_rot.shape[0], num_heads, rank, rot_dim, float(scale), int(window or 0),
-          int(single_tokens))
+          _ptr(tok_pos), _ptr(tok_slot), _ptr(out), tokens, num_heads, rank, rot_dim, float(scale), int(window or 0),
+          int(single_tokens), int(chunk_keys), int(chunks), _ptr(part_o), _ptr(part_ml))
 
 
 def latent_gate(o: torch.Tensor, gate: torch.Tensor, gate_column: int, per_head: bool, out: torch.Tensor, *, heads: int,

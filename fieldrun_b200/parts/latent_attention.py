@@ -164,9 +164,20 @@ class LatentAttention(Mixer):
         return linear(out, self.w_o)
 
     def attend(self, ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, line: LineView, o_lat: torch.Tensor) -> None:
-        """bfloat16 and key rows the tensor-core kernel takes: that kernel, for prompts and single tokens alike; the
-        general kernel (float32 arithmetic, any sizes) otherwise."""
+        """bfloat16 and key rows the tensor-core kernel takes: that kernel, for prompts and single tokens alike (single
+        tokens over a line of more than 256 keys in chunks of keys side by side); the general kernel (float32
+        arithmetic, any sizes) otherwise."""
         if self.dtype == torch.bfloat16 and ops.latent_mma_takes(self.kv_rank, self.rot_dim):
+            chunk_keys, chunks = ops.latent_key_chunks(line.page_table.shape[1]) if ctx.is_decode else (0, 0)
+            if chunks > 1:                               # single tokens: a block per (token, chunk of keys), then the join
+                tokens = q_rot.shape[0]
+                part_o = ctx.buffer("latent.part_o", (chunks, self.num_heads, tokens, self.kv_rank), torch.float32)
+                part_ml = ctx.buffer("latent.part_ml", (chunks, self.num_heads, tokens, 2), torch.float32)
+                ops.latent_attention_mma(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
+                                         num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim,
+                                         scale=self.softmax_scale, window=self.window, single_tokens=True,
+                                         chunk_keys=chunk_keys, part_o=part_o, part_ml=part_ml)
+                return
             ops.latent_attention_mma(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
                                      num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim,
                                      scale=self.softmax_scale, window=self.window, single_tokens=ctx.is_decode)
