@@ -36,7 +36,7 @@ GROUPS: dict[str, tuple[str, ...]] = {
     "products": ("experts_tc.cu",),
     "recurrent": ("gla.cu",),
     "scans": ("scans.cu",),
-    "latent": ("latent_attention.cu",),
+    "latent": ("latent_attention.cu", "latent_attention_tc.cu"),
     "extras": ("attention_decode_noalloc.cu", "wait_probe.cu"),
 }
 SHARED_SOURCE = "errors.cu"

@@ -70,6 +70,7 @@ _SIGNATURES = {
     "frb_latent_attention": "pppipipppiiiifi",
     "frb_latent_gate": "ppiiipiiii",
     "frb_latent_attention_mma": "ppppipppiiiifiiiipp",
+    "frb_latent_attention_tc": "pppipipppiiiifip",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -85,7 +86,7 @@ _ENTRY_GROUPS = {
                "frb_dyt_norm", "frb_rms_blend", "frb_concat_rows", "frb_add_row_vector", "frb_head_gate", "frb_embed_pair_rows",
                "frb_token_side_gate", "frb_add_rms_normed", "frb_add_typed_copy"),
     "latent": ("frb_latent_prepare", "frb_latent_queries", "frb_latent_attention", "frb_latent_gate",
-               "frb_latent_attention_mma"),
+               "frb_latent_attention_mma", "frb_latent_attention_tc"),
     "attention": ("frb_attention_decode_mma", "frb_attention_prefill_mma", "frb_attention_decode_tma", "frb_attention_prefill_tc"),
     "streams": ("frb_weight_stream", "frb_expert_gemm_mma"),
     "experts": ("frb_router_topk", "frb_expert_plan", "frb_expert_combine", "frb_expert_gemm_generic", "frb_route_plan_small",
@@ -931,6 +932,14 @@ _WAIT_CODES = {
     16: "prompt attention: the softmax waiting for the scores",
     18: "prompt attention: the correction waiting for the step before",
     19: "prompt attention: the epilogue waiting for the last steps",
+    21: "latent attention: the producer waiting for the scores of the page before",
+    22: "latent attention: the producer waiting for the sums of the page before",
+    23: "latent attention: the MMA thread waiting for the queries",
+    24: "latent attention: the MMA thread waiting for a page's pieces",
+    25: "latent attention: the MMA thread waiting for the probabilities",
+    26: "latent attention: the softmax waiting for the scores",
+    27: "latent attention: the correction waiting for the page before",
+    28: "latent attention: the epilogue waiting for the last page",
     99: "the wait probe, whose wait is meant to run out",
 }
 
@@ -1186,6 +1195,35 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torc
     _call("frb_latent_attention_mma", _ptr(q_lat), _ptr(q_rot), _ptr(k_pages), _ptr(page_table), page_table.shape[1],
           _ptr(tok_pos), _ptr(tok_slot), _ptr(out), tokens, num_heads, rank, rot_dim, float(scale), int(window or 0),
           int(single_tokens), int(chunk_keys), int(chunks), _ptr(part_o), _ptr(part_ml))
+
+
+def latent_tc_takes(rank: int, rot_dim: int) -> bool:
+    """Whether the tcgen05 kernel takes key rows of ``rank`` + ``rot_dim`` entries (bfloat16 only): pieces of 64 entries,
+    at most nine of them, and a latent that halves into pieces beyond 256."""
+    return (rank >= 64 and rank % 64 == 0 and rot_dim >= 64 and rot_dim % 64 == 0 and rank + rot_dim <= 576
+            and (rank <= 256 or rank % 128 == 0))
+
+
+def latent_attention_tc(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Tensor, page_table: torch.Tensor,
+                        tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int, rank: int,
+                        rot_dim: int, scale: float, window: Optional[int]) -> None:
+    """``latent_attention`` on tcgen05 tensor cores, bfloat16, for many tokens a sequence: tiles of 128 (head, token) rows
+    over pages of 64 shared key rows.  A sequence's tokens lie together, in rising positions."""
+    if not (q_lat.dtype == q_rot.dtype == k_pages.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("the tcgen05 latent attention takes bfloat16 queries, cache and output")
+    if not latent_tc_takes(rank, rot_dim):
+        raise KernelError(f"the tcgen05 latent attention does not take key rows of {rank} + {rot_dim} entries")
+    tokens = q_rot.shape[0]
+    if tuple(q_lat.shape) != (num_heads, tokens, rank) or tuple(out.shape) != (num_heads, tokens, rank) or \
+            tuple(q_rot.shape) != (tokens, num_heads, rot_dim) or k_pages.shape[-1] != rank + rot_dim:
+        raise KernelError(f"tcgen05 latent attention: queries {tuple(q_lat.shape)} and {tuple(q_rot.shape)}, key rows of "
+                          f"{k_pages.shape[-1]}, output {tuple(out.shape)} for {num_heads} heads, {rank} + {rot_dim} entries")
+    for t in (q_lat, q_rot, k_pages, out):
+        if not t.is_contiguous():
+            raise KernelError("the tcgen05 latent attention takes contiguous tensors")
+    _call("frb_latent_attention_tc", _ptr(q_lat), _ptr(q_rot), _ptr(k_pages), k_pages.shape[0], _ptr(page_table),
+          page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), tokens, num_heads, rank, rot_dim, float(scale),
+          int(window or 0), _ptr(tc_status(q_lat.device)))
 
 
 def latent_gate(o: torch.Tensor, gate: torch.Tensor, gate_column: int, per_head: bool, out: torch.Tensor, *, heads: int,

@@ -164,9 +164,14 @@ class LatentAttention(Mixer):
         return linear(out, self.w_o)
 
     def attend(self, ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, line: LineView, o_lat: torch.Tensor) -> None:
-        """bfloat16 and key rows the tensor-core kernel takes: that kernel, for prompts and single tokens alike (single
-        tokens over a line of more than 256 keys in chunks of keys side by side); the general kernel (float32
-        arithmetic, any sizes) otherwise."""
+        """bfloat16: prompts over key rows in pieces of 64 entries go to the tcgen05 kernel; other key rows that the
+        mma.sync kernel takes, and single tokens, go to that one (single tokens over a line of more than 256 keys in
+        chunks of keys side by side); the general kernel (float32 arithmetic, any sizes) otherwise."""
+        if self.dtype == torch.bfloat16 and not ctx.is_decode and ops.latent_tc_takes(self.kv_rank, self.rot_dim):
+            ops.latent_attention_tc(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
+                                    num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim,
+                                    scale=self.softmax_scale, window=self.window)
+            return
         if self.dtype == torch.bfloat16 and ops.latent_mma_takes(self.kv_rank, self.rot_dim):
             chunk_keys, chunks = ops.latent_key_chunks(line.page_table.shape[1]) if ctx.is_decode else (0, 0)
             if chunks > 1:                               # single tokens: a block per (token, chunk of keys), then the join

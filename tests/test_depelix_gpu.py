@@ -121,16 +121,20 @@ def run_latent_attention(kernel, case, queries, heads, scale, window):
     return f64(out), want
 
 
-LATENT_KERNELS = ["latent_attention", "latent_attention_mma"]
+LATENT_KERNELS = ["latent_attention", "latent_attention_mma", "latent_attention_tc"]
 # (heads, rank, rot) that the tensor-core kernel takes, and some that only the general one does
 MMA_SHAPES = [(4, 64, 32), (16, 128, 64), (5, 512, 64), (1, 32, 16), (40, 256, 32)]
 GENERAL_SHAPES = [(3, 40, 8), (2, 24, 12), (9, 100, 0), (4, 18, 6)]
+# pieces of 64 entries for the tcgen05 kernel: a latent in one block and in two halves, 8 to 1 tokens a tile, heads that
+# do not fill a tile's rows, more heads than a tile has rows, two pieces of rotated entries
+TC_SHAPES = [(16, 128, 64), (5, 512, 64), (3, 64, 64), (40, 256, 64), (32, 192, 128), (130, 64, 64), (1, 384, 64)]
 
 
 def latent_shapes():
     return [("latent_attention", "float32", s) for s in MMA_SHAPES[:3] + GENERAL_SHAPES] + \
            [("latent_attention", "bfloat16", s) for s in MMA_SHAPES[:2] + GENERAL_SHAPES[:2]] + \
-           [("latent_attention_mma", "bfloat16", s) for s in MMA_SHAPES]
+           [("latent_attention_mma", "bfloat16", s) for s in MMA_SHAPES] + \
+           [("latent_attention_tc", "bfloat16", s) for s in TC_SHAPES]
 
 
 @pytest.mark.parametrize("kernel,dtype,shape", latent_shapes())
@@ -151,13 +155,14 @@ def test_attention_over_shared_key_rows_in_prompts_and_single_tokens(kernel, dty
     close(got, want, KERNEL_TOL[dtype], f"{kernel}: portions")
 
 
-@pytest.mark.parametrize("kernel,dtype", [("latent_attention", "float32"), ("latent_attention", "bfloat16"), ("latent_attention_mma", "bfloat16")])
+@pytest.mark.parametrize("kernel,dtype", [("latent_attention", "float32"), ("latent_attention", "bfloat16"), ("latent_attention_mma", "bfloat16"),
+                                          ("latent_attention_tc", "bfloat16")])
 @pytest.mark.parametrize("window", [None, 7, 64, 72, 129])
 def test_a_key_far_back_or_at_the_windows_edge_is_seen_or_not(kernel, dtype, window):
     """One key row is made to match one query so well that it takes nearly all of the softmax if it is seen at all: the
     first key of a long sequence, the last key inside the window and the first one outside it, for a query in a prompt
     and for a single token."""
-    heads, rank, rot = 4, 64, 32
+    heads, rank, rot = (4, 64, 64) if kernel == "latent_attention_tc" else (4, 64, 32)
     rng = np.random.default_rng(5)
     n = 700
     for target_back in ([n - 1, 1, 300] if window is None else [window - 1, window, window + 1, 0]):
