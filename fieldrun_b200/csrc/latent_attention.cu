@@ -351,6 +351,10 @@ __device__ __forceinline__ void lm_copies_done() { asm volatile("cp.async.wait_a
 template <int MT, int NTW>
 __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(LatentMmaParams p) {
     after_previous_kernel();
+    if (p.chunk_keys > 0) {                              // single tokens in chunks of keys: a chunk without a visible key ends here
+        const int pos = p.tok_pos[blockIdx.x], z = (int)blockIdx.z;
+        if (pos < z * p.chunk_keys || (z + 1) * p.chunk_keys - 1 < first_visible_key(pos, p.window, 0) / LM_KEYS * LM_KEYS) return;
+    }
     constexpr int M = 16 * MT;
     constexpr int RT_S = MT >= 4 ? MT / 4 : 1;           // row tiles of a warp in the score phase
     extern __shared__ __align__(16) unsigned char lm_smem[];
@@ -600,27 +604,58 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
     }
 }
 
-// out[h][t][:] = sum_z 2^(m_z - m) o_z / sum_z 2^(m_z - m) l_z over the chunks that hold visible keys of token t
-__global__ void __launch_bounds__(128) latent_combine_kernel(LatentMmaParams p) {
+// out[h][t][:] = sum_z 2^(m_z - m) o_z / sum_z 2^(m_z - m) l_z over the chunks that hold visible keys of token t (at most
+// LM_MAX_CHUNKS).  The threads weigh the chunks, a thread every 128th; then every thread sums four entries over the
+// chunks in their order.  The order of every sum depends on the token's position and the window only.
+#define LM_MAX_CHUNKS 1024
+#define LM_COMBINE_THREADS 128
+__global__ void __launch_bounds__(LM_COMBINE_THREADS) latent_combine_kernel(LatentMmaParams p) {
     after_previous_kernel();
+    __shared__ float weight[LM_MAX_CHUNKS];
+    __shared__ float red[2][LM_COMBINE_THREADS / 32];
     const int t = blockIdx.x, head = blockIdx.y, T = p.num_tokens, H = p.num_heads, R = p.rank;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pos = p.tok_pos[t];
     const int z_lo = first_visible_key(pos, p.window, 0) / LM_KEYS * LM_KEYS / p.chunk_keys, z_hi = pos / p.chunk_keys;
+    const int count = min(z_hi - z_lo + 1, LM_MAX_CHUNKS);
+    const float* ml0 = p.part_ml + 2 * (((size_t)z_lo * H + head) * T + t);
+    const size_t ml_step = (size_t)2 * H * T;
     float m = -INFINITY;
-    for (int z = z_lo; z <= z_hi; ++z) m = fmaxf(m, p.part_ml[2 * (((size_t)z * H + head) * T + t)]);
-    float total = 0.f;
-    for (int z = z_lo; z <= z_hi; ++z) {
-        const float* ml = p.part_ml + 2 * (((size_t)z * H + head) * T + t);
-        if (ml[1] > 0.f) total += exp2f(ml[0] - m) * ml[1];
+    for (int z = tid; z < count; z += LM_COMBINE_THREADS) {
+        const float2 ml = *reinterpret_cast<const float2*>(ml0 + z * ml_step);
+        if (ml.y > 0.f) m = fmaxf(m, ml.x);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[0][warp] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
+    float total = 0.f;
+    for (int z = tid; z < count; z += LM_COMBINE_THREADS) {
+        const float2 ml = *reinterpret_cast<const float2*>(ml0 + z * ml_step);
+        const float w = ml.y > 0.f ? exp2f(ml.x - m) : 0.f;
+        weight[z] = w;
+        total += w * ml.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if (lane == 0) red[1][warp] = total;
+    __syncthreads();
+    total = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
     const float inv = total > 0.f ? 1.0f / total : 0.f;
-    for (int d = threadIdx.x; d < R; d += blockDim.x) {
-        float acc = 0.f;
-        for (int z = z_lo; z <= z_hi; ++z) {
-            const size_t row = ((size_t)z * H + head) * T + t;
-            if (p.part_ml[2 * row + 1] > 0.f) acc += exp2f(p.part_ml[2 * row] - m) * p.part_o[row * R + d];
+    const float* first = p.part_o + (((size_t)z_lo * H + head) * T + t) * R;
+    const size_t step = (size_t)H * T * R;                     // from a chunk's part to the next chunk's
+    for (int d = 4 * tid; d < R; d += 4 * LM_COMBINE_THREADS) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < count; ++z) {
+            const float wz = weight[z];
+            if (wz == 0.f) continue;
+            const float4 v = *reinterpret_cast<const float4*>(first + z * step + d);
+            acc.x = fmaf(wz, v.x, acc.x); acc.y = fmaf(wz, v.y, acc.y); acc.z = fmaf(wz, v.z, acc.z); acc.w = fmaf(wz, v.w, acc.w);
         }
-        p.out[((size_t)head * T + t) * R + d] = __float2bfloat16(acc * inv);
+        bf16* dst = p.out + ((size_t)head * T + t) * R + d;
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     }
 }
 
@@ -649,8 +684,8 @@ FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const
     p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.out = (bf16*)out; p.scale2 = scale * 1.4426950408889634f; p.window = window;
     p.max_pages = max_pages; p.num_tokens = num_tokens; p.num_heads = num_heads; p.rank = rank; p.rot_dim = rot_dim;
     p.tokens_per_block = per_block;
-    FRB_CHECK_ARG(chunk_keys == 0 || (single_tokens && chunk_keys % LM_KEYS == 0 && num_chunks >= 1 && part_o && part_ml),
-                  "latent attention in chunks of %d keys (%d of them): single tokens, a multiple of %d, and room for the parts",
+    FRB_CHECK_ARG(chunk_keys == 0 || (single_tokens && chunk_keys % LM_KEYS == 0 && num_chunks >= 1 && num_chunks <= LM_MAX_CHUNKS && part_o && part_ml),
+                  "latent attention in chunks of %d keys (%d of them, at most 1024): single tokens, a multiple of %d, and room for the parts",
                   chunk_keys, num_chunks, LM_KEYS);
     p.chunk_keys = chunk_keys; p.part_o = (float*)part_o; p.part_ml = (float*)part_ml;
     const int DS = rank + rot_dim + 8;
@@ -671,6 +706,6 @@ FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const
     if (rows == 16) FRB_LATENT_MMA_ROWS(1);
     else if (rows == 32) FRB_LATENT_MMA_ROWS(2);
     else FRB_LATENT_MMA_ROWS(4);
-    if (chunk_keys > 0) launch_dependent(latent_combine_kernel, dim3(num_tokens, num_heads), dim3(128), 0, stream, p);
+    if (chunk_keys > 0) launch_dependent(latent_combine_kernel, dim3(num_tokens, num_heads), dim3(LM_COMBINE_THREADS), 0, stream, p);
     FRB_RETURN_LAUNCH("latent_attention_mma");
 }

@@ -1152,13 +1152,14 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Te
           float(scale), int(window or 0))
 
 
-def latent_key_chunks(max_pages: int) -> tuple[int, int]:
-    """(keys a chunk, chunks) for single tokens over a line of ``max_pages`` pages: chunks of 256 keys, larger ones where
-    the line is so long that there would be more than 32.  It depends on the line's size only, never on a step."""
+def latent_key_chunks(max_pages: int) -> int:
+    """Keys a chunk for single tokens over a line of ``max_pages`` pages: 256, more where the line is so long that there
+    would be more than 1,024 chunks.  It depends on the line's size only, never on a step, so the cuts always lie at the
+    same keys."""
     keys = 256
-    while keys * 32 < max_pages * 64:
+    while keys * 1024 < max_pages * 64:
         keys *= 2
-    return keys, max(1, -(-max_pages * 64 // keys))
+    return keys
 
 
 def latent_mma_takes(rank: int, rot_dim: int) -> bool:
@@ -1175,7 +1176,8 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torc
     rows.  A sequence's tokens lie together, in rising positions.  ``single_tokens``: every token is another sequence
     (a block per token instead of a block per run of tokens); with ``chunk_keys`` > 0 a block per (token, chunk of that
     many keys, cut at fixed multiples), the chunks' sums in ``part_o`` [chunks, heads, T, rank] and their (maximum, sum
-    of weights) in ``part_ml`` [chunks, heads, T, 2], both float32, joined by a second kernel."""
+    of weights) in ``part_ml`` [chunks, heads, T, 2], both float32, joined by a second kernel.  The chunks must cover
+    every token's position: keys beyond the last chunk are not read."""
     if not (q_lat.dtype == q_rot.dtype == k_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("the tensor-core latent attention takes bfloat16 queries, cache and output")
     if not latent_mma_takes(rank, rot_dim):
@@ -1187,8 +1189,6 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torc
         _want(part_o, torch.float32, "the chunks' sums")
         _want(part_ml, torch.float32, "the chunks' maxima and sums of weights")
         chunks = part_o.shape[0]
-        if chunks * chunk_keys < page_table.shape[1] * 64:         # a page holds 64 keys (FRB_PAGE)
-            raise KernelError(f"{chunks} chunks of {chunk_keys} keys do not cover {page_table.shape[1]} pages")
         if tuple(part_o.shape) != (chunks, num_heads, tokens, rank) or tuple(part_ml.shape) != (chunks, num_heads, tokens, 2):
             raise KernelError(f"parts of shapes {tuple(part_o.shape)} and {tuple(part_ml.shape)} for {chunks} chunks, "
                               f"{num_heads} heads, {tokens} tokens and a latent of {rank}")

@@ -173,7 +173,8 @@ class LatentAttention(Mixer):
                                     scale=self.softmax_scale, window=self.window)
             return
         if self.dtype == torch.bfloat16 and ops.latent_mma_takes(self.kv_rank, self.rot_dim):
-            chunk_keys, chunks = ops.latent_key_chunks(line.page_table.shape[1]) if ctx.is_decode else (0, 0)
+            chunk_keys = ops.latent_key_chunks(line.page_table.shape[1])
+            chunks = -(-ctx.max_kv_len // chunk_keys) if ctx.is_decode else 0      # over the step's longest sequence
             if chunks > 1:                               # single tokens: a block per (token, chunk of keys), then the join
                 tokens = q_rot.shape[0]
                 part_o = ctx.buffer("latent.part_o", (chunks, self.num_heads, tokens, self.kv_rank), torch.float32)
