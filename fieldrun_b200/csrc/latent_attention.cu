@@ -309,6 +309,7 @@ FRB_API int frb_latent_gate(const float* o, const float* gate, int gate_stride, 
 #define LM_THREADS 512
 #define LM_KEYS 32
 #define LM_PSTRIDE 40
+#define LM_DECODE_STAGES 4     // tiles of key rows in shared memory in the form for single tokens of at most 16 heads
 
 struct LatentMmaParams {
     const bf16* q_lat;          // [H, T, R]
@@ -345,6 +346,12 @@ __device__ __forceinline__ void lm_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 __device__ __forceinline__ void lm_copy16(bf16* to, const bf16* from) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(to);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(from) : "memory");
+}
+// 2^x by the special-function unit (relative error about 2^-22; -inf and anything below -126 give 0)
+__device__ __forceinline__ float lm_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ void lm_copies_done() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
@@ -604,6 +611,210 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
     }
 }
 
+// latent_decode_mma: single tokens, at most 16 heads a block (one row tile).  The form above leaves twelve of sixteen
+// warps idle while four compute the scores, and passes maxima, weights and factors through shared memory with three
+// barriers a tile.  Here every warp takes a key tile (w & 3) and a quarter of the D entries (w >> 2): S = sum of four
+// partial products, exchanged once through shared memory.  Every warp then holds the whole 16 x 32 tile of scores in
+// the accumulator layout, computes the same maxima, weights and sums, and uses its weights directly as the A operand
+// of O += P C for its own latent entries (the accumulator layout of two key tiles is the A layout of sixteen keys).
+// Two barriers a tile: the tile has landed, the partial products are there.
+template <int NTW>
+__global__ void __launch_bounds__(LM_THREADS, 1) latent_decode_mma_kernel(LatentMmaParams p) {
+    after_previous_kernel();
+    const int tok = blockIdx.x, h0 = blockIdx.y * 16, T = p.num_tokens, H = p.num_heads;
+    const int pos = p.tok_pos[tok];
+    const int lo = first_visible_key(pos, p.window, 0);
+    int j_begin = lo / LM_KEYS * LM_KEYS, j_last = pos;
+    if (p.chunk_keys > 0) {                              // a chunk without a visible key ends here
+        j_begin = max(j_begin, (int)blockIdx.z * p.chunk_keys);
+        j_last = min(j_last, ((int)blockIdx.z + 1) * p.chunk_keys - 1);
+        if (j_last < j_begin) return;
+    }
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    const int R = p.rank, D = p.rank + p.rot_dim, DS = D + 8, chunks = D / 8;
+    bf16* q_s = reinterpret_cast<bf16*>(lm_smem);        // [16][DS]
+    bf16* k_s = q_s + (size_t)16 * DS;                   // [LM_DECODE_STAGES][LM_KEYS][DS]
+    float4* part = reinterpret_cast<float4*>(k_s + (size_t)LM_DECODE_STAGES * LM_KEYS * DS);     // [4 quarters][4 key tiles][32 lanes]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+
+    for (int i = tid; i < 16 * chunks; i += LM_THREADS) {
+        const int r = i / chunks, c = i - r * chunks, head = h0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (head < H) {
+            const int d = c * 8;
+            const bf16* src = d < R ? p.q_lat + ((size_t)head * T + tok) * R + d
+                                    : p.q_rot + ((size_t)tok * H + head) * p.rot_dim + (d - R);
+            v = *reinterpret_cast<const uint4*>(src);
+        }
+        *reinterpret_cast<uint4*>(q_s + (size_t)r * DS + c * 8) = v;
+    }
+    const int* table = p.page_table + (size_t)p.tok_slot[tok] * p.max_pages;
+    const int tiles = (j_last - j_begin) / LM_KEYS + 1;
+    const int nt = warp & 3, quarter = warp >> 2;
+    const int steps = D / 16, steps_each = (steps + 3) / 4;
+    const int step_lo = min(steps, quarter * steps_each), step_hi = min(steps, step_lo + steps_each);
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[NTW][4];
+#pragma unroll
+    for (int n = 0; n < NTW; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+
+    // A tile of 32 key rows is 37 KB; one of them on its way at a time leaves the memory idle most of the time (a block
+    // per SM, about a microsecond from request to arrival).  So LM_DECODE_STAGES - 1 tiles are on their way while one
+    // is used.  Every turn commits one group of copies, an empty one after the last tile, so that "all but the newest
+    // LM_DECODE_STAGES - 2 groups have landed" always means "this turn's tile has landed".
+    // a thread's copies of a tile: 16 bytes c of key row `key`, the next one LM_THREADS places on (no division a copy)
+    const int copy_key0 = tid / chunks, copy_c0 = tid - copy_key0 * chunks;
+    const int copy_key_step = LM_THREADS / chunks, copy_c_step = LM_THREADS - copy_key_step * chunks;
+    auto fetch_tile = [&](int tile) {
+        if (tile < tiles) {
+            const int j0 = j_begin + tile * LM_KEYS;
+            const int page = table[j0 / FRB_PAGE];
+            bf16* dst = k_s + (size_t)(tile % LM_DECODE_STAGES) * LM_KEYS * DS;
+            const bf16* src = p.k_pages + ((size_t)(page < 0 ? 0 : page) * FRB_PAGE + j0 % FRB_PAGE) * D;
+            for (int key = copy_key0, c = copy_c0; key < LM_KEYS;) {
+                if (page >= 0) lm_copy16(dst + (size_t)key * DS + c * 8, src + (size_t)key * D + c * 8);
+                else *reinterpret_cast<uint4*>(dst + (size_t)key * DS + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+                key += copy_key_step;
+                c += copy_c_step;
+                if (c >= chunks) { c -= chunks; ++key; }
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    for (int ahead = 0; ahead < LM_DECODE_STAGES - 1; ++ahead) fetch_tile(ahead);
+    for (int tile = 0; tile < tiles; ++tile) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(LM_DECODE_STAGES - 2) : "memory");
+        __syncthreads();                                 // the tile is here; everyone is done with the tile before
+        fetch_tile(tile + LM_DECODE_STAGES - 1);         // into the stage of the tile before
+        const bf16* kb = k_s + (size_t)(tile % LM_DECODE_STAGES) * LM_KEYS * DS;
+        const int j0 = j_begin + tile * LM_KEYS;
+
+        // this warp's part of the scores: key tile nt, entries [16 step_lo, 16 step_hi)
+        float s_even[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const bf16* k_at = kb + (size_t)(nt * 8 + (lane & 7)) * DS + (lane >> 3) * 8;
+            const bf16* q_at = q_s + (size_t)(lane & 15) * DS + (lane >> 4) * 8;
+            int st = step_lo;
+            for (; st + 2 <= step_hi; st += 2) {
+                uint32_t b0, b1, b2, b3, a0, a1, a2, a3, a4, a5, a6, a7;
+                lm_ldmatrix_x4(b0, b1, b2, b3, k_at + st * 16);
+                lm_ldmatrix_x4(a0, a1, a2, a3, q_at + st * 16);
+                lm_ldmatrix_x4(a4, a5, a6, a7, q_at + st * 16 + 16);
+                lm_mma(s_even, a0, a1, a2, a3, b0, b1);
+                lm_mma(s_odd, a4, a5, a6, a7, b2, b3);
+            }
+            if (st < step_hi) {
+                uint32_t b0, b1, a0, a1, a2, a3;
+                lm_ldmatrix_x2(b0, b1, kb + (size_t)(nt * 8 + (lane & 7)) * DS + ((lane >> 3) & 1) * 8 + st * 16);
+                lm_ldmatrix_x4(a0, a1, a2, a3, q_at + st * 16);
+                lm_mma(s_even, a0, a1, a2, a3, b0, b1);
+            }
+        }
+        part[(quarter * 4 + nt) * 32 + lane] = make_float4(s_even[0] + s_odd[0], s_even[1] + s_odd[1], s_even[2] + s_odd[2], s_even[3] + s_odd[3]);
+        __syncthreads();                                 // the partial products are there
+
+        // the whole tile of scores, in every warp: s[j] = key tile j, rows g (entries 0, 1) and g + 8 (entries 2, 3)
+        float s[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 p0 = part[(0 * 4 + j) * 32 + lane], p1 = part[(1 * 4 + j) * 32 + lane];
+            const float4 p2 = part[(2 * 4 + j) * 32 + lane], p3 = part[(3 * 4 + j) * 32 + lane];
+            s[j][0] = (p0.x + p1.x) + (p2.x + p3.x); s[j][1] = (p0.y + p1.y) + (p2.y + p3.y);
+            s[j][2] = (p0.z + p1.z) + (p2.z + p3.z); s[j][3] = (p0.w + p1.w) + (p2.w + p3.w);
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+        if (j0 >= lo && j0 + LM_KEYS - 1 <= pos) {       // every key of the tile is visible (the scale is positive)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = j0 + 8 * j + 2 * tq + (e & 1);
+                    if (key < lo || key > pos) s[j][e] = -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+                }
+        }
+        float factor[2], m_sub[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h] * p.scale2);
+            factor[h] = m_new == -INFINITY ? 1.f : lm_exp2(m_run[h] - m_new);
+            m_run[h] = m_new;
+            m_sub[h] = m_new == -INFINITY ? 0.f : m_new;
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float w = lm_exp2(fmaf(s[j][e], p.scale2, -m_sub[e >> 1]));      // a masked key: 2^-inf = 0
+                s[j][e] = w;
+                sum[e >> 1] += w;
+            }
+        l_run[0] = l_run[0] * factor[0] + sum[0];
+        l_run[1] = l_run[1] * factor[1] + sum[1];
+#pragma unroll
+        for (int n = 0; n < NTW; ++n) { o[n][0] *= factor[0]; o[n][1] *= factor[0]; o[n][2] *= factor[1]; o[n][3] *= factor[1]; }
+        // sums: O += P C for this warp's latent entries; the weights of key tiles 2 kk and 2 kk + 1 are the A operand
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            const __nv_bfloat162 w0 = __floats2bfloat162_rn(s[2 * kk][0], s[2 * kk][1]), w1 = __floats2bfloat162_rn(s[2 * kk][2], s[2 * kk][3]);
+            const __nv_bfloat162 w2 = __floats2bfloat162_rn(s[2 * kk + 1][0], s[2 * kk + 1][1]), w3 = __floats2bfloat162_rn(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&w0), a1 = *reinterpret_cast<const uint32_t*>(&w1);
+            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&w2), a3 = *reinterpret_cast<const uint32_t*>(&w3);
+            uint32_t pb[NTW][2];
+#pragma unroll
+            for (int n = 0; n < NTW; ++n) {
+                const int d0 = (warp + LM_THREADS / 32 * n) * 8;
+                if (d0 < R) lm_ldmatrix_x2_trans(pb[n][0], pb[n][1], kb + (size_t)(kk * 16 + (lane & 15)) * DS + d0);
+            }
+#pragma unroll
+            for (int n = 0; n < NTW; ++n) {
+                const int d0 = (warp + LM_THREADS / 32 * n) * 8;
+                if (d0 < R) lm_mma(o[n], a0, a1, a2, a3, pb[n][0], pb[n][1]);
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int head = h0 + g + 8 * h;
+        if (head >= H) continue;
+        if (p.chunk_keys > 0) {
+            const size_t row = ((size_t)blockIdx.z * H + head) * T + tok;
+            if (warp == 0 && tq == 0) { p.part_ml[2 * row] = m_run[h]; p.part_ml[2 * row + 1] = l_run[h]; }
+#pragma unroll
+            for (int n = 0; n < NTW; ++n) {
+                const int d0 = (warp + LM_THREADS / 32 * n) * 8;
+                if (d0 < R) *reinterpret_cast<float2*>(p.part_o + row * R + d0 + 2 * tq) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+            }
+            continue;
+        }
+        const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
+        bf16* dst = p.out + ((size_t)head * T + tok) * R;
+#pragma unroll
+        for (int n = 0; n < NTW; ++n) {
+            const int d0 = (warp + LM_THREADS / 32 * n) * 8;
+            if (d0 < R)
+                *reinterpret_cast<__nv_bfloat162*>(dst + d0 + 2 * tq) = __floats2bfloat162_rn(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        }
+    }
+}
+
 // out[h][t][:] = sum_z 2^(m_z - m) o_z / sum_z 2^(m_z - m) l_z over the chunks that hold visible keys of token t (at most
 // LM_MAX_CHUNKS).  The threads weigh the chunks, a thread every 128th; then every thread sums four entries over the
 // chunks in their order.  The order of every sum depends on the token's position and the window only.
@@ -659,6 +870,15 @@ __global__ void __launch_bounds__(LM_COMBINE_THREADS) latent_combine_kernel(Late
     }
 }
 
+// the join for the kernels of this library that leave parts by chunks of keys (latent_attention_tc.cu has one too)
+void latent_combine_launch(const int* tok_pos, int window, int chunk_keys, float* part_o, float* part_ml, void* out,
+                           int num_tokens, int num_heads, int rank, cudaStream_t stream) {
+    LatentMmaParams p = {};
+    p.tok_pos = tok_pos; p.window = window; p.chunk_keys = chunk_keys; p.part_o = part_o; p.part_ml = part_ml;
+    p.out = (bf16*)out; p.num_tokens = num_tokens; p.num_heads = num_heads; p.rank = rank;
+    launch_dependent(latent_combine_kernel, dim3(num_tokens, num_heads), dim3(LM_COMBINE_THREADS), 0, stream, p);
+}
+
 FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const void* k_pages, const int* page_table,
                                      int max_pages, const int* tok_pos, const int* tok_slot, void* out, int num_tokens,
                                      int num_heads, int rank, int rot_dim, float scale, int window, int single_tokens,
@@ -666,6 +886,7 @@ FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const
     if (num_tokens == 0) return 0;
     FRB_CHECK_ARG(rank >= 8 && rank <= 512 && rank % 8 == 0 && (rank + rot_dim) % 16 == 0 && rot_dim >= 0,
                   "latent attention on tensor cores: a latent of %d and a key part of %d entries", rank, rot_dim);
+    FRB_CHECK_ARG(scale > 0.f, "latent attention on tensor cores: a softmax scale of %g is not positive", (double)scale);
     int padded_heads = 1;
     while (padded_heads < num_heads && padded_heads < 64) padded_heads *= 2;
     int rows, per_block;
@@ -703,7 +924,19 @@ FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const
         else if (rank <= 256) FRB_LATENT_MMA(MT, 2);                                                                   \
         else FRB_LATENT_MMA(MT, 4);                                                                                    \
     } while (0)
-    if (rows == 16) FRB_LATENT_MMA_ROWS(1);
+    if (single_tokens && rows == 16) {                   // one row tile: the form with every warp on the scores
+        const size_t smem_one = ((size_t)16 * DS + (size_t)LM_DECODE_STAGES * LM_KEYS * DS) * sizeof(bf16) + (size_t)16 * 32 * sizeof(float4);
+#define FRB_LATENT_DECODE(NTW)                                                                                         \
+    do {                                                                                                               \
+        auto kernel = latent_decode_mma_kernel<NTW>;                                                                   \
+        if (smem_one > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_one); \
+        launch_dependent(kernel, grid, dim3(LM_THREADS), smem_one, stream, p);                                         \
+    } while (0)
+        if (rank <= 128) FRB_LATENT_DECODE(1);
+        else if (rank <= 256) FRB_LATENT_DECODE(2);
+        else FRB_LATENT_DECODE(4);
+#undef FRB_LATENT_DECODE
+    } else if (rows == 16) FRB_LATENT_MMA_ROWS(1);
     else if (rows == 32) FRB_LATENT_MMA_ROWS(2);
     else FRB_LATENT_MMA_ROWS(4);
     if (chunk_keys > 0) launch_dependent(latent_combine_kernel, dim3(num_tokens, num_heads), dim3(LM_COMBINE_THREADS), 0, stream, p);

@@ -68,6 +68,10 @@ struct LatentTcParams {
     int tokens_per_block, heads_per_block;      // TQ x HB = 128
     int half_rank;              // RH: the latent entries of one block
     uint32_t tmem_cols;
+    int chunk_pages;            // > 0 (single tokens, TQ = 1): grid.x counts (token, chunk) pairs; a block takes the pages
+    int num_chunks;             // [z, z + 1) * chunk_pages of its token and leaves unnormalised sums [Z, H, T, R] and
+    float* part_o;              // (maximum in use, sum of weights) [Z, H, T, 2] for the join (latent_combine_kernel)
+    float* part_ml;
 };
 
 // the run of tokens of one sequence that starts at token `begin` of the block
@@ -75,7 +79,7 @@ struct LatentTcRun {
     int begin, end, slot, first_page, pages;
 };
 
-__device__ __forceinline__ LatentTcRun lt_run(const LatentTcParams& p, int t0, int begin) {
+__device__ __forceinline__ LatentTcRun lt_run(const LatentTcParams& p, int t0, int begin, int chunk) {
     LatentTcRun r;
     const int TQ = p.tokens_per_block, T = p.num_tokens;
     r.begin = begin;
@@ -89,7 +93,12 @@ __device__ __forceinline__ LatentTcRun lt_run(const LatentTcParams& p, int t0, i
         hi = max(hi, pos);
     }
     r.first_page = lo / FRB_PAGE;
-    r.pages = hi / FRB_PAGE - r.first_page + 1;
+    int last_page = hi / FRB_PAGE;
+    if (p.chunk_pages > 0) {
+        r.first_page = max(r.first_page, chunk * p.chunk_pages);
+        last_page = min(last_page, (chunk + 1) * p.chunk_pages - 1);
+    }
+    r.pages = last_page - r.first_page + 1;              // none (or less) if the chunk holds no visible key
     return r;
 }
 
@@ -105,7 +114,12 @@ latent_attention_tc_kernel(const __grid_constant__ CUtensorMap map_ql, const __g
     let_next_kernel_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int TQ = p.tokens_per_block, HB = p.heads_per_block, T = p.num_tokens, H = p.num_heads;
-    const int t0 = blockIdx.x * TQ, h0 = blockIdx.y * HB;
+    const int chunk = p.chunk_pages > 0 ? (int)blockIdx.x % p.num_chunks : 0;
+    const int t0 = p.chunk_pages > 0 ? (int)blockIdx.x / p.num_chunks : (int)blockIdx.x * TQ, h0 = blockIdx.y * HB;
+    if (p.chunk_pages > 0) {                                   // a chunk without a visible key ends here (every thread
+        wait_for_previous_kernel();                            // alike, before any barrier and any tensor memory)
+        if (lt_run(p, t0, 0, chunk).pages <= 0) return;
+    }
     const int R = p.rank, RH = p.half_rank;
     const int latent_pieces = R / 64, pieces = (R + p.rot_dim) / 64;
     const int own0 = (int)blockIdx.z * (RH / 64), own1 = own0 + RH / 64;      // this block's pieces of the latent
@@ -143,7 +157,7 @@ latent_attention_tc_kernel(const __grid_constant__ CUtensorMap map_ql, const __g
             int n = 0, begin = 0;
             bool ok = true;
             while (ok && begin < TQ && t0 + begin < T) {
-                const LatentTcRun run = lt_run(p, t0, begin);
+                const LatentTcRun run = lt_run(p, t0, begin, chunk);
                 const int* table = p.page_table + (size_t)run.slot * p.max_pages;
                 for (int j = 0; j < run.pages && ok; ++j, ++n) {
                     const int page = max(table[run.first_page + j], 0);
@@ -172,7 +186,7 @@ latent_attention_tc_kernel(const __grid_constant__ CUtensorMap map_ql, const __g
             if (!ok) atomicExch(p.status, 23);
             int n = 0, begin = 0;
             while (ok && begin < TQ && t0 + begin < T) {
-                const LatentTcRun run = lt_run(p, t0, begin);
+                const LatentTcRun run = lt_run(p, t0, begin, chunk);
                 for (int j = 0; j < run.pages && ok; ++j, ++n) {
                     if (!bar_wait(&first_full, n & 1, failed)) { atomicExch(p.status, 24); ok = false; break; }
                     fence_after_sync();
@@ -218,7 +232,7 @@ latent_attention_tc_kernel(const __grid_constant__ CUtensorMap map_ql, const __g
         bool ok = true;
         int n = 0, begin = 0;
         while (begin < TQ && t0 + begin < T) {
-            const LatentTcRun run = lt_run(p, t0, begin);
+            const LatentTcRun run = lt_run(p, t0, begin, chunk);
             const bool valid = tok < T && head < H && ti >= run.begin && ti < run.end;
             const int hi = valid ? p.tok_pos[tok] : -1;
             const int lo = valid ? first_visible_key(hi, p.window, 0) : 0;
@@ -293,15 +307,26 @@ latent_attention_tc_kernel(const __grid_constant__ CUtensorMap map_ql, const __g
             // the run's last P C has ended: this row's part of the output
             if (!bar_wait(&pv_done, (n - 1) & 1, failed)) { if (ok && lane == 0) atomicExch(p.status, 28); ok = false; }
             fence_after_sync();
-            const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+            const float inv = p.chunk_pages > 0 ? 1.f : l_sum > 0.f ? 1.0f / l_sum : 0.f;
             const bool write = valid && ok && !*failed;
+            float* part = nullptr;
+            if (p.chunk_pages > 0 && write) {
+                const size_t part_row = ((size_t)chunk * H + head) * T + tok;
+                part = p.part_o + part_row * R + (size_t)blockIdx.z * RH;
+                if (blockIdx.z == 0) { p.part_ml[2 * part_row] = m_used; p.part_ml[2 * part_row + 1] = l_sum; }
+            }
             bf16* dst = p.out + ((size_t)(valid ? head : 0) * T + (valid ? tok : 0)) * R + (size_t)blockIdx.z * RH;
 #pragma unroll 1
             for (int c = 0; c < RH / 16; ++c) {
                 uint32_t o[16];
                 tmem_ld16(o_mine + 16 * c, o);
                 tmem_wait_ld();
-                if (write) {
+                if (part) {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4)
+                        *reinterpret_cast<float4*>(part + 16 * c + i) = make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]),
+                                                                                   __uint_as_float(o[i + 2]), __uint_as_float(o[i + 3]));
+                } else if (write) {
                     uint4 lo4, hi4;
                     lo4.x = pack_bf16x2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
                     lo4.y = pack_bf16x2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
@@ -351,20 +376,32 @@ static bool lt_map_heads_tokens(CUtensorMap* map, const void* base, uint64_t hea
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+void latent_combine_launch(const int* tok_pos, int window, int chunk_keys, float* part_o, float* part_ml, void* out,
+                           int num_tokens, int num_heads, int rank, cudaStream_t stream);     // latent_attention.cu
+
 // q_lat bf16 [H, T, R]; q_rot bf16 [T, H, P]; k_pages bf16 [pages, 1, 64, R + P]; out bf16 [H, T, R].  A sequence's
 // tokens lie together, in rising positions.  R and P multiples of 64, R + P at most 576, R a multiple of 128 beyond 256.
-// status: one int on the device, zero before the call.
+// chunk_keys > 0: every token is another sequence; a block takes one token's heads (of 128 rows the heads fill the
+// first ones: the tensor cores have time to spare where the key rows come from memory once for a single token) and
+// the keys [z, z + 1) * chunk_keys (a multiple of 64) for one of num_chunks z; the chunks cover every position;
+// part_o float32 [num_chunks, H, T, R] and part_ml float32 [num_chunks, H, T, 2] take the parts, a second kernel joins
+// them.  status: one int on the device, zero before the call.
 FRB_API int frb_latent_attention_tc(const void* q_lat, const void* q_rot, const void* k_pages, int num_pages,
                                     const int* page_table, int max_pages, const int* tok_pos, const int* tok_slot, void* out,
                                     int num_tokens, int num_heads, int rank, int rot_dim, float scale, int window, int* status,
-                                    cudaStream_t stream) {
+                                    int chunk_keys, int num_chunks, void* part_o, void* part_ml, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
     FRB_CHECK_ARG(rank >= 64 && rank % 64 == 0 && rot_dim >= 64 && rot_dim % 64 == 0 && rank + rot_dim <= 576 &&
                   (rank <= 256 || rank % 128 == 0),
                   "tcgen05 latent attention: a latent of %d and a key part of %d entries", rank, rot_dim);
     FRB_CHECK_ARG(scale > 0.f, "tcgen05 latent attention: a softmax scale of %g is not positive", (double)scale);
+    FRB_CHECK_ARG(chunk_keys == 0 || (chunk_keys % FRB_PAGE == 0 && num_chunks >= 1 && num_chunks <= 1024 && part_o && part_ml &&
+                                      num_heads <= LT_ROWS),
+                  "tcgen05 latent attention in chunks of %d keys (%d of them, at most 1024): a multiple of %d, at most %d heads, and room for the parts",
+                  chunk_keys, num_chunks, FRB_PAGE, LT_ROWS);
     int heads_per_block = 1;
     while (heads_per_block < num_heads && heads_per_block < LT_ROWS) heads_per_block *= 2;
+    if (chunk_keys > 0) heads_per_block = LT_ROWS;
     const int tokens_per_block = LT_ROWS / heads_per_block;
     const int halves = rank > 256 ? 2 : 1, half_rank = rank / halves, pieces = (rank + rot_dim) / 64;
     CUtensorMap map_ql, map_qr, map_k;
@@ -378,9 +415,12 @@ FRB_API int frb_latent_attention_tc(const void* q_lat, const void* q_rot, const 
     p.num_heads = num_heads; p.rank = rank; p.rot_dim = rot_dim; p.tokens_per_block = tokens_per_block;
     p.heads_per_block = heads_per_block; p.half_rank = half_rank;
     p.tmem_cols = LT_O_COL + half_rank <= 128 ? 128 : LT_O_COL + half_rank <= 256 ? 256 : 512;
+    p.chunk_pages = chunk_keys / FRB_PAGE; p.num_chunks = num_chunks; p.part_o = (float*)part_o; p.part_ml = (float*)part_ml;
     const size_t smem = (size_t)pieces * (LT_Q_PIECE + LT_K_PIECE) + 1024;
-    dim3 grid((num_tokens + tokens_per_block - 1) / tokens_per_block, (num_heads + heads_per_block - 1) / heads_per_block, halves);
+    dim3 grid(chunk_keys > 0 ? num_tokens * num_chunks : (num_tokens + tokens_per_block - 1) / tokens_per_block,
+              (num_heads + heads_per_block - 1) / heads_per_block, halves);
     cudaFuncSetAttribute(latent_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_dependent(latent_attention_tc_kernel, grid, dim3(LT_THREADS), smem, stream, map_ql, map_qr, map_k, p);
+    if (chunk_keys > 0) latent_combine_launch(tok_pos, window, chunk_keys, p.part_o, p.part_ml, out, num_tokens, num_heads, rank, stream);
     FRB_RETURN_LAUNCH("latent_attention_tc");
 }

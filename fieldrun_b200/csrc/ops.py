@@ -70,7 +70,7 @@ _SIGNATURES = {
     "frb_latent_attention": "pppipipppiiiifi",
     "frb_latent_gate": "ppiiipiiii",
     "frb_latent_attention_mma": "ppppipppiiiifiiiipp",
-    "frb_latent_attention_tc": "pppipipppiiiifip",
+    "frb_latent_attention_tc": "pppipipppiiiifipiipp",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -1206,9 +1206,13 @@ def latent_tc_takes(rank: int, rot_dim: int) -> bool:
 
 def latent_attention_tc(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch.Tensor, page_table: torch.Tensor,
                         tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int, rank: int,
-                        rot_dim: int, scale: float, window: Optional[int]) -> None:
-    """``latent_attention`` on tcgen05 tensor cores, bfloat16, for many tokens a sequence: tiles of 128 (head, token) rows
-    over pages of 64 shared key rows.  A sequence's tokens lie together, in rising positions."""
+                        rot_dim: int, scale: float, window: Optional[int], chunk_keys: int = 0,
+                        part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+    """``latent_attention`` on tcgen05 tensor cores, bfloat16: tiles of 128 (head, token) rows over pages of 64 shared key
+    rows.  A sequence's tokens lie together, in rising positions.  With ``chunk_keys`` > 0 every token is another
+    sequence (at most 128 heads): a block per (token, chunk of that many keys, cut at fixed multiples), the chunks' sums in
+    ``part_o`` [chunks, heads, T, rank] and their (maximum, sum of weights) in ``part_ml`` [chunks, heads, T, 2], both
+    float32, joined by a second kernel.  The chunks must cover every token's position."""
     if not (q_lat.dtype == q_rot.dtype == k_pages.dtype == out.dtype == torch.bfloat16):
         raise KernelError("the tcgen05 latent attention takes bfloat16 queries, cache and output")
     if not latent_tc_takes(rank, rot_dim):
@@ -1221,9 +1225,19 @@ def latent_attention_tc(q_lat: torch.Tensor, q_rot: torch.Tensor, k_pages: torch
     for t in (q_lat, q_rot, k_pages, out):
         if not t.is_contiguous():
             raise KernelError("the tcgen05 latent attention takes contiguous tensors")
+    chunks = 0
+    if chunk_keys:
+        if part_o is None or part_ml is None or num_heads > 128:
+            raise KernelError("tcgen05 latent attention in chunks of keys: at most 128 heads, and it needs room for the parts")
+        _want(part_o, torch.float32, "the chunks' sums")
+        _want(part_ml, torch.float32, "the chunks' maxima and sums of weights")
+        chunks = part_o.shape[0]
+        if tuple(part_o.shape) != (chunks, num_heads, tokens, rank) or tuple(part_ml.shape) != (chunks, num_heads, tokens, 2):
+            raise KernelError(f"parts of shapes {tuple(part_o.shape)} and {tuple(part_ml.shape)} for {chunks} chunks, "
+                              f"{num_heads} heads, {tokens} tokens and a latent of {rank}")
     _call("frb_latent_attention_tc", _ptr(q_lat), _ptr(q_rot), _ptr(k_pages), k_pages.shape[0], _ptr(page_table),
           page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), tokens, num_heads, rank, rot_dim, float(scale),
-          int(window or 0), _ptr(tc_status(q_lat.device)))
+          int(window or 0), _ptr(tc_status(q_lat.device)), int(chunk_keys), int(chunks), _ptr(part_o), _ptr(part_ml))
 
 
 def latent_gate(o: torch.Tensor, gate: torch.Tensor, gate_column: int, per_head: bool, out: torch.Tensor, *, heads: int,

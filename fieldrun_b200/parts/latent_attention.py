@@ -165,29 +165,29 @@ class LatentAttention(Mixer):
 
     def attend(self, ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, line: LineView, o_lat: torch.Tensor) -> None:
         """bfloat16: prompts over key rows in pieces of 64 entries go to the tcgen05 kernel; other key rows that the
-        mma.sync kernel takes, and single tokens, go to that one (single tokens over a line of more than 256 keys in
-        chunks of keys side by side); the general kernel (float32 arithmetic, any sizes) otherwise."""
-        if self.dtype == torch.bfloat16 and not ctx.is_decode and ops.latent_tc_takes(self.kv_rank, self.rot_dim):
-            ops.latent_attention_tc(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
-                                    num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim,
-                                    scale=self.softmax_scale, window=self.window)
-            return
-        if self.dtype == torch.bfloat16 and ops.latent_mma_takes(self.kv_rank, self.rot_dim):
-            chunk_keys = ops.latent_key_chunks(line.page_table.shape[1])
-            chunks = -(-ctx.max_kv_len // chunk_keys) if ctx.is_decode else 0      # over the step's longest sequence
-            if chunks > 1:                               # single tokens: a block per (token, chunk of keys), then the join
-                tokens = q_rot.shape[0]
-                part_o = ctx.buffer("latent.part_o", (chunks, self.num_heads, tokens, self.kv_rank), torch.float32)
-                part_ml = ctx.buffer("latent.part_ml", (chunks, self.num_heads, tokens, 2), torch.float32)
-                ops.latent_attention_mma(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
-                                         num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim,
-                                         scale=self.softmax_scale, window=self.window, single_tokens=True,
-                                         chunk_keys=chunk_keys, part_o=part_o, part_ml=part_ml)
+        mma.sync kernel takes, and single tokens, go to that one (single tokens over more than one chunk of keys in
+        chunks side by side, then the join); the general kernel (float32 arithmetic, any sizes) otherwise.  The tcgen05
+        kernel has a form for single tokens in chunks too; measured, it is the slower one (it fills 128 rows with one
+        token's heads and computes the scores once per half of the latent), so no step uses it."""
+        if self.dtype == torch.bfloat16:
+            common = dict(num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim, scale=self.softmax_scale,
+                          window=self.window)
+            if not ctx.is_decode and ops.latent_tc_takes(self.kv_rank, self.rot_dim):
+                ops.latent_attention_tc(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat, **common)
                 return
-            ops.latent_attention_mma(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
-                                     num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim,
-                                     scale=self.softmax_scale, window=self.window, single_tokens=ctx.is_decode)
-            return
+            if ops.latent_mma_takes(self.kv_rank, self.rot_dim):
+                chunk_keys = ops.latent_key_chunks(line.page_table.shape[1])
+                chunks = -(-ctx.max_kv_len // chunk_keys) if ctx.is_decode else 0      # over the step's longest sequence
+                if chunks > 1:                           # single tokens: a block per (token, chunk of keys), then the join
+                    tokens = q_rot.shape[0]
+                    part_o = ctx.buffer("latent.part_o", (chunks, self.num_heads, tokens, self.kv_rank), torch.float32)
+                    part_ml = ctx.buffer("latent.part_ml", (chunks, self.num_heads, tokens, 2), torch.float32)
+                    ops.latent_attention_mma(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
+                                             single_tokens=True, chunk_keys=chunk_keys, part_o=part_o, part_ml=part_ml, **common)
+                else:
+                    ops.latent_attention_mma(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
+                                             single_tokens=ctx.is_decode, **common)
+                return
         ops.latent_attention(q_lat, q_rot, line.keys, line.page_table, ctx.tok_pos, ctx.tok_slot, o_lat,
                              num_heads=self.num_heads, rank=self.kv_rank, rot_dim=self.rot_dim, scale=self.softmax_scale,
                              window=self.window)

@@ -11,6 +11,8 @@ per expert, as in a step of 16k prompt tokens),
 loads weights into registers, kept for inner sizes that are no multiple of 64), ``attention_decode`` (pages by TMA),
 ``attention_decode_mma`` (pages loaded into registers), ``attention_prefill``
 (mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries; ``attention_prefill_tc_long``: one prompt of 16,384 tokens),
+``latent_attention_prefill`` (attention over shared key rows of 512 + 64 entries, tcgen05; ``latent_attention_prefill_mma``: the
+mma.sync kernel), ``latent_attention_decode`` and ``latent_attention_decode_small`` (single tokens in chunks of keys, with the join; ``..._mma``: the mma.sync kernel),
 ``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens),
 ``step_decode`` and ``step_prefill`` (two whole layers through the engine, for launch lists; not part of ``all``),
 ``step_timeline`` (a replayed decode step's kernels with their start and end times, from the profiler that ships with torch;
@@ -152,6 +154,59 @@ def attention(kind: str, launches: int) -> dict:
         ops.tc_status_check(dev)
     flops = 4 * HEADS * HEAD_DIM * context * (context + 1) // 2
     return {"case": f"attention_{kind}", "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
+
+
+LATENT_HEADS, LATENT_RANK, LATENT_ROT = 16, 512, 64
+
+
+def latent_attention(kind: str, launches: int) -> dict:
+    """Attention over shared key rows [latent ; rotated part] (16 heads, 512 + 64 entries): ``prefill`` one prompt of 2,048
+    tokens on tcgen05, ``prefill_mma`` the same on mma.sync, ``decode`` one token for each of 32 sequences over 4,096-token
+    caches in chunks of 256 keys on tcgen05 (the kernel and the join), ``decode_small`` the same for 8 sequences of 2,048;
+    ``decode_mma`` and ``decode_small_mma`` the mma.sync kernel on the same."""
+    dev = torch.device("cuda")
+    heads, rank, rot = LATENT_HEADS, LATENT_RANK, LATENT_ROT
+    batch, context = {"decode": (32, 4096), "decode_mma": (32, 4096), "decode_small": (8, 2048), "decode_small_mma": (8, 2048)}.get(kind, (1, 2048))
+    pages_per = context // 64
+    pages = batch * pages_per
+    keys = (torch.randn(pages, 1, 64, rank + rot, device=dev) * 0.3).to(torch.bfloat16)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(batch, pages_per).contiguous()
+    scale = (128 + rot) ** -0.5
+    if kind.startswith("decode"):
+        tokens = batch
+        positions = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+        slots = torch.arange(batch, dtype=torch.int32, device=dev)
+    else:
+        tokens = context
+        positions = torch.arange(context, dtype=torch.int32, device=dev)
+        slots = torch.zeros(context, dtype=torch.int32, device=dev)
+    q_lat = torch.randn(heads, tokens, rank, device=dev).to(torch.bfloat16)
+    q_rot = torch.randn(tokens, heads, rot, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q_lat)
+    common = dict(num_heads=heads, rank=rank, rot_dim=rot, scale=scale, window=None)
+    if kind.startswith("decode"):
+        chunk_keys = ops.latent_key_chunks(pages_per)
+        chunks = -(-context // chunk_keys)
+        part_o = torch.empty(chunks, heads, tokens, rank, dtype=torch.float32, device=dev)
+        part_ml = torch.empty(chunks, heads, tokens, 2, dtype=torch.float32, device=dev)
+        if kind.endswith("_mma"):
+            launch = lambda: ops.latent_attention_mma(q_lat, q_rot, keys, table, positions, slots, out, single_tokens=True,
+                                                      chunk_keys=chunk_keys, part_o=part_o, part_ml=part_ml, **common)
+        else:
+            launch = lambda: ops.latent_attention_tc(q_lat, q_rot, keys, table, positions, slots, out, chunk_keys=chunk_keys,
+                                                     part_o=part_o, part_ml=part_ml, **common)
+        ms = _time(launch, launches)
+        ops.tc_status_check(dev)
+        return {"case": "latent_attention_" + kind, "ms": round(ms, 4), "batch": batch, "context": context,
+                "key_rows_gb_per_s": round(keys.numel() * 2 / ms / 1e6, 1)}
+    if kind == "prefill":
+        launch = lambda: ops.latent_attention_tc(q_lat, q_rot, keys, table, positions, slots, out, **common)
+    else:
+        launch = lambda: ops.latent_attention_mma(q_lat, q_rot, keys, table, positions, slots, out, **common)
+    ms = _time(launch, launches)
+    ops.tc_status_check(dev)
+    flops = 2 * heads * (2 * rank + rot) * context * (context + 1) // 2
+    return {"case": "latent_attention_" + kind, "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
 
 
 def small_kernels(launches: int, tokens: int) -> dict:
@@ -447,6 +502,12 @@ CASES = {
     "attention_prefill": lambda n: attention("prefill", n),
     "attention_prefill_tc": lambda n: attention("prefill_tc", n),
     "attention_prefill_tc_long": lambda n: attention("prefill_tc_long", n),
+    "latent_attention_prefill": lambda n: latent_attention("prefill", n),
+    "latent_attention_prefill_mma": lambda n: latent_attention("prefill_mma", n),
+    "latent_attention_decode": lambda n: latent_attention("decode", n),
+    "latent_attention_decode_small": lambda n: latent_attention("decode_small", n),
+    "latent_attention_decode_mma": lambda n: latent_attention("decode_mma", n),
+    "latent_attention_decode_small_mma": lambda n: latent_attention("decode_small_mma", n),
     "step_decode": lambda n, batch=8: whole_step("decode", n, batch),
     "step_prefill": lambda n: whole_step("prefill", n),
     "step_timeline": lambda n, batch=8: step_timeline(n, batch),

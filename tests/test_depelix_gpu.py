@@ -189,8 +189,8 @@ def test_a_key_far_back_or_at_the_windows_edge_is_seen_or_not(kernel, dtype, win
             close(f64(out), want, KERNEL_TOL[dtype], f"{kernel}: key {target_back} back, window {window}")
 
 
-def single_tokens_in_chunks(case, queries, q_lat, q_rot, heads, scale, window, chunk_keys):
-    """The tensor-core kernel in its form for single tokens, the keys cut into chunks of ``chunk_keys``: [heads, rows, rank]."""
+def single_tokens_in_chunks(case, queries, q_lat, q_rot, heads, scale, window, chunk_keys, kernel="latent_attention_mma"):
+    """A tensor-core kernel in its form for single tokens, the keys cut into chunks of ``chunk_keys``: [heads, rows, rank]."""
     o = ops()
     count = len(queries)
     pages, table = case.device()
@@ -198,18 +198,23 @@ def single_tokens_in_chunks(case, queries, q_lat, q_rot, heads, scale, window, c
     out = torch.full((heads, count, case.rank), float("nan"), dtype=torch.bfloat16, device=DEV)
     part_o = torch.full((chunks, heads, count, case.rank), float("nan"), dtype=torch.float32, device=DEV)
     part_ml = torch.full((chunks, heads, count, 2), float("nan"), dtype=torch.float32, device=DEV)
-    o.latent_attention_mma(dev(q_lat.astype(np.float32), torch.bfloat16), dev(q_rot.astype(np.float32), torch.bfloat16), pages, table,
-                           i32([p for _, p in queries]), i32([case.slots[b] for b, _ in queries]), out, num_heads=heads,
-                           rank=case.rank, rot_dim=case.rot, scale=scale, window=window, single_tokens=True,
-                           chunk_keys=chunk_keys, part_o=part_o, part_ml=part_ml)
+    more = {"single_tokens": True} if kernel == "latent_attention_mma" else {}
+    getattr(o, kernel)(dev(q_lat.astype(np.float32), torch.bfloat16), dev(q_rot.astype(np.float32), torch.bfloat16), pages, table,
+                       i32([p for _, p in queries]), i32([case.slots[b] for b, _ in queries]), out, num_heads=heads,
+                       rank=case.rank, rot_dim=case.rot, scale=scale, window=window, chunk_keys=chunk_keys, part_o=part_o,
+                       part_ml=part_ml, **more)
     torch.cuda.synchronize()
+    o.tc_status_check(torch.device(DEV))
     return f64(out)
 
 
-@pytest.mark.parametrize("shape", [(4, 64, 32), (16, 128, 64), (5, 512, 64), (40, 256, 32)])
+CHUNKED = [("latent_attention_mma", s, c) for s in [(4, 64, 32), (16, 128, 64), (5, 512, 64), (40, 256, 32)] for c in (32, 256)] + \
+          [("latent_attention_tc", s, c) for s in [(16, 128, 64), (5, 512, 64), (3, 64, 64), (40, 256, 64), (128, 64, 128)] for c in (64, 256)]
+
+
+@pytest.mark.parametrize("kernel,shape,chunk_keys", CHUNKED)
 @pytest.mark.parametrize("window", [None, 1, 33, 256, 300])
-@pytest.mark.parametrize("chunk_keys", [32, 256])
-def test_single_tokens_over_keys_in_chunks_side_by_side(shape, window, chunk_keys):
+def test_single_tokens_over_keys_in_chunks_side_by_side(kernel, shape, window, chunk_keys):
     """One token a sequence, its keys cut at fixed multiples of the chunk: sequences that end just before, on and just
     after a cut, one shorter than a chunk, one of a single key; then every token alone, which must give the same bits."""
     heads, rank, rot = shape
@@ -219,19 +224,20 @@ def test_single_tokens_over_keys_in_chunks_side_by_side(shape, window, chunk_key
     queries = [(b, n - 1) for b, n in enumerate(lengths)]
     q_lat = rounded(rng.normal(size=(heads, len(queries), rank)), "bfloat16")
     q_rot = rounded(rng.normal(size=(len(queries), heads, rot)), "bfloat16")
-    got = single_tokens_in_chunks(case, queries, q_lat, q_rot, heads, 0.2, window, chunk_keys)
+    got = single_tokens_in_chunks(case, queries, q_lat, q_rot, heads, 0.2, window, chunk_keys, kernel)
     want = np.stack([case.plain(b, p, q_lat[:, t], q_rot[t], 0.2, window) for t, (b, p) in enumerate(queries)], axis=1)
-    close(got, want, KERNEL_TOL["bfloat16"], f"single tokens in chunks of {chunk_keys}")
+    close(got, want, KERNEL_TOL["bfloat16"], f"{kernel}: single tokens in chunks of {chunk_keys}")
     for t in (3, 5):
-        alone = single_tokens_in_chunks(case, queries[t:t + 1], q_lat[:, t:t + 1], q_rot[t:t + 1], heads, 0.2, window, chunk_keys)
+        alone = single_tokens_in_chunks(case, queries[t:t + 1], q_lat[:, t:t + 1], q_rot[t:t + 1], heads, 0.2, window, chunk_keys, kernel)
         assert np.array_equal(alone[:, 0], got[:, t]), f"token {t} alone and in a step of {len(queries)}"
 
 
+@pytest.mark.parametrize("kernel", ["latent_attention_mma", "latent_attention_tc"])
 @pytest.mark.parametrize("window", [None, 300, 301])
-def test_single_token_whose_far_key_lies_in_another_chunk(window):
+def test_single_token_whose_far_key_lies_in_another_chunk(kernel, window):
     """The first key of the first chunk is made to match the query; the query sits two chunks later.  It takes nearly all
     of the softmax if the window reaches it, and nothing otherwise."""
-    heads, rank, rot, n = 4, 64, 32, 557
+    heads, rank, rot, n = (4, 64, 64, 557) if kernel == "latent_attention_tc" else (4, 64, 32, 557)
     rng = np.random.default_rng(11)
     case = LatentCase(rng, [n], rank, rot, "bfloat16", spread=0.3)
     j = 256
@@ -240,7 +246,7 @@ def test_single_token_whose_far_key_lies_in_another_chunk(window):
     queries = [(0, n - 1)]
     q_lat = np.repeat(case.rows[0][j][None, None, :rank], heads, axis=0) * 0.5
     q_rot = np.repeat(case.rows[0][j][None, None, rank:], heads, axis=1) * 0.5
-    got = single_tokens_in_chunks(case, queries, q_lat, q_rot, heads, 0.25, window, 256)
+    got = single_tokens_in_chunks(case, queries, q_lat, q_rot, heads, 0.25, window, 256, kernel)
     want = case.plain(0, n - 1, q_lat[:, 0], q_rot[0], 0.25, window)[:, None]
     seen = window is None or n - 1 - j < window
     assert (np.abs(want[:, 0] - case.rows[0][j][:rank]).max() < 1e-3) == seen
