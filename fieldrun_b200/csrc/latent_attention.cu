@@ -309,6 +309,7 @@ FRB_API int frb_latent_gate(const float* o, const float* gate, int gate_stride, 
 #define LM_THREADS 512
 #define LM_KEYS 32
 #define LM_PSTRIDE 40
+#define LM_DECODE_QSTEPS 9      // steps of 16 entries a warp takes of the scores: a quarter of (R + P) / 16 <= 36
 #define LM_DECODE_STAGES 4     // tiles of key rows in shared memory in the form for single tokens of at most 16 heads
 
 struct LatentMmaParams {
@@ -660,6 +661,8 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_decode_mma_kernel(Latent
     for (int n = 0; n < NTW; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    const int my_steps = step_hi - step_lo;              // at most LM_DECODE_QSTEPS (D <= 576)
+    uint32_t qf[LM_DECODE_QSTEPS][4];                    // the A operands of this warp's steps, the same for every tile
 
     // A tile of 32 key rows is 37 KB; one of them on its way at a time leaves the memory idle most of the time (a block
     // per SM, about a microsecond from request to arrival).  So LM_DECODE_STAGES - 1 tiles are on their way while one
@@ -686,6 +689,12 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_decode_mma_kernel(Latent
     };
 
     for (int ahead = 0; ahead < LM_DECODE_STAGES - 1; ++ahead) fetch_tile(ahead);
+    __syncthreads();                                     // the queries are in shared memory
+#pragma unroll
+    for (int i = 0; i < LM_DECODE_QSTEPS; ++i) {
+        qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+        if (i < my_steps) lm_ldmatrix_x4(qf[i][0], qf[i][1], qf[i][2], qf[i][3], q_s + (size_t)(lane & 15) * DS + (lane >> 4) * 8 + (step_lo + i) * 16);
+    }
     for (int tile = 0; tile < tiles; ++tile) {
         asm volatile("cp.async.wait_group %0;\n" ::"n"(LM_DECODE_STAGES - 2) : "memory");
         __syncthreads();                                 // the tile is here; everyone is done with the tile before
@@ -693,25 +702,22 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_decode_mma_kernel(Latent
         const bf16* kb = k_s + (size_t)(tile % LM_DECODE_STAGES) * LM_KEYS * DS;
         const int j0 = j_begin + tile * LM_KEYS;
 
-        // this warp's part of the scores: key tile nt, entries [16 step_lo, 16 step_hi)
+        // this warp's part of the scores: key tile nt, entries [16 step_lo, 16 step_hi); its queries wait in registers
         float s_even[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
         {
-            const bf16* k_at = kb + (size_t)(nt * 8 + (lane & 7)) * DS + (lane >> 3) * 8;
-            const bf16* q_at = q_s + (size_t)(lane & 15) * DS + (lane >> 4) * 8;
-            int st = step_lo;
-            for (; st + 2 <= step_hi; st += 2) {
-                uint32_t b0, b1, b2, b3, a0, a1, a2, a3, a4, a5, a6, a7;
-                lm_ldmatrix_x4(b0, b1, b2, b3, k_at + st * 16);
-                lm_ldmatrix_x4(a0, a1, a2, a3, q_at + st * 16);
-                lm_ldmatrix_x4(a4, a5, a6, a7, q_at + st * 16 + 16);
-                lm_mma(s_even, a0, a1, a2, a3, b0, b1);
-                lm_mma(s_odd, a4, a5, a6, a7, b2, b3);
-            }
-            if (st < step_hi) {
-                uint32_t b0, b1, a0, a1, a2, a3;
-                lm_ldmatrix_x2(b0, b1, kb + (size_t)(nt * 8 + (lane & 7)) * DS + ((lane >> 3) & 1) * 8 + st * 16);
-                lm_ldmatrix_x4(a0, a1, a2, a3, q_at + st * 16);
-                lm_mma(s_even, a0, a1, a2, a3, b0, b1);
+            const bf16* k_at = kb + (size_t)(nt * 8 + (lane & 7)) * DS + (lane >> 3) * 8 + step_lo * 16;
+#pragma unroll
+            for (int i = 0; i < LM_DECODE_QSTEPS; i += 2) {
+                if (i + 1 < my_steps) {
+                    uint32_t b0, b1, b2, b3;
+                    lm_ldmatrix_x4(b0, b1, b2, b3, k_at + i * 16);
+                    lm_mma(s_even, qf[i][0], qf[i][1], qf[i][2], qf[i][3], b0, b1);
+                    if (i + 1 < LM_DECODE_QSTEPS) lm_mma(s_odd, qf[i + 1][0], qf[i + 1][1], qf[i + 1][2], qf[i + 1][3], b2, b3);
+                } else if (i < my_steps) {
+                    uint32_t b0, b1;
+                    lm_ldmatrix_x2(b0, b1, kb + (size_t)(nt * 8 + (lane & 7)) * DS + ((lane >> 3) & 1) * 8 + (step_lo + i) * 16);
+                    lm_mma(s_even, qf[i][0], qf[i][1], qf[i][2], qf[i][3], b0, b1);
+                }
             }
         }
         part[(quarter * 4 + nt) * 32 + lane] = make_float4(s_even[0] + s_odd[0], s_even[1] + s_odd[1], s_even[2] + s_odd[2], s_even[3] + s_odd[3]);
@@ -924,7 +930,7 @@ FRB_API int frb_latent_attention_mma(const void* q_lat, const void* q_rot, const
         else if (rank <= 256) FRB_LATENT_MMA(MT, 2);                                                                   \
         else FRB_LATENT_MMA(MT, 4);                                                                                    \
     } while (0)
-    if (single_tokens && rows == 16) {                   // one row tile: the form with every warp on the scores
+    if (single_tokens && rows == 16 && ((rank + rot_dim) / 16 + 3) / 4 <= LM_DECODE_QSTEPS) {     // one row tile: the form with every warp on the scores
         const size_t smem_one = ((size_t)16 * DS + (size_t)LM_DECODE_STAGES * LM_KEYS * DS) * sizeof(bf16) + (size_t)16 * 32 * sizeof(float4);
 #define FRB_LATENT_DECODE(NTW)                                                                                         \
     do {                                                                                                               \
