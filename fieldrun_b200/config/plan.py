@@ -37,6 +37,9 @@ class LayerSpec:
     mixer_norm: PartSpec
     feed_forward_norm: Optional[PartSpec]
     addition: Optional[PartSpec] = None
+    # norms behind the sublayers, for a block that has a norm on both sides of each (``sandwich_norm``)
+    mixer_out_norm: Optional[PartSpec] = None
+    feed_forward_out_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

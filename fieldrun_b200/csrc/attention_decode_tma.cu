@@ -162,8 +162,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         }
                         // this thread's columns 2 t + (e & 1) of the tile are keys 32 m + 8 t + 4 (e & 1) + u of the page
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            s[4 * m + u][e] = fmaf(acc[e], p.scale2, slope2[e >> 1] * (float)(key_base + 32 * m + 8 * t + 4 * (e & 1) + u - hi_key));
+                        for (int e = 0; e < 4; ++e) {
+                            const float scaled = p.cap2 > 0.f ? capped_score2(acc[e], p.cap_scale, p.cap2) : acc[e] * p.scale2;
+                            s[4 * m + u][e] = fmaf(slope2[e >> 1], (float)(key_base + 32 * m + 8 * t + 4 * (e & 1) + u - hi_key), scaled);
+                        }
                     }
             }
             __syncwarp();
@@ -323,7 +325,7 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
                                      const int* page_table, int max_pages, const int* seq_pos, const int* seq_slot,
                                      float* part_o, float* part_ml, void* out, int num_seqs, int num_heads, int num_kv_heads,
                                      int head_dim, float scale, int window, int max_chunks, int chunks_per_block, int* status,
-                                     const float* slopes, int chunk, const float* sinks, cudaStream_t stream) {
+                                     const float* slopes, int chunk, const float* sinks, float softcap, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
@@ -344,6 +346,7 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads; p.max_chunks = parts; p.status = status; p.slopes = slopes;
     p.chunk = chunk; p.sinks = sinks;
+    p.cap_scale = softcap > 0.f ? scale / softcap : 0.f; p.cap2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     params.chunks_per_block = chunks_per_block; params.status = status;
     static const int early = [] { const char* v = getenv("FIELDRUN_B200_ATTENTION_EARLY"); return !(v && v[0] == '0'); }();
     params.early = early;

@@ -11,7 +11,8 @@
 // at position i (a slope per query head; null: none).  Three more, each off unless given: `chunk` (the query at i
 // sees only keys of its own chunk, floor(j / chunk) == floor(i / chunk), chunks counted from position 0), `sinks`
 // (a number per query head whose exponential joins the softmax's denominator, with no key and no value: it is not
-// scaled and counts once) and `gate` (the head's output is multiplied by sigmoid(gate[t, h])).
+// scaled and counts once), `gate` (the head's output is multiplied by sigmoid(gate[t, h])) and `softcap` (the scaled
+// score s of every key becomes softcap * tanh(s / softcap) before anything else is done with it).
 #include "common.cuh"
 
 struct AttnParams {
@@ -27,6 +28,7 @@ struct AttnParams {
     const int* tok_slot;      // [T]
     void* out;                // [T, nh * vd]
     float scale;
+    float softcap;            // > 0: the scaled score s becomes softcap * tanh(s / softcap); 0: none
     int window;               // 0: every earlier key
     int max_pages, num_heads, num_kv_heads, head_dim, v_dim;
 };
@@ -90,7 +92,9 @@ __global__ void attention_generic_kernel(AttnParams p) {
                 const float* qr = q_rows + warp * hd;
                 const float* kr = k_tile + lane * (hd + 1);
                 for (int d = 0; d < hd; ++d) s += qr[d] * kr[d];
-                s = valid ? s * p.scale - slope * (float)(pos - j) : -INFINITY;
+                s *= p.scale;
+                if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+                s = valid ? s - slope * (float)(pos - j) : -INFINITY;
                 const float m_new = fmaxf(m, warp_max(s));
                 const float corr = expf(m - m_new);
                 const float pj = valid ? expf(s - m_new) : 0.f;
@@ -132,7 +136,7 @@ FRB_API int frb_attention_generic(const void* q, const void* k_pages, const void
                                   const int* page_table, int max_pages, const int* tok_pos, const int* tok_slot,
                                   void* out, int num_tokens, int num_heads, int num_kv_heads, int head_dim,
                                   float scale, int window, int v_dim, const float* slopes, int chunk, const float* sinks,
-                                  const float* gate, int gate_stride, cudaStream_t stream) {
+                                  const float* gate, int gate_stride, float softcap, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
     if (v_dim <= 0) v_dim = head_dim;
     FRB_CHECK_ARG(v_dim <= 256, "attention: v_dim %d is outside 1..256", v_dim);
@@ -144,7 +148,7 @@ FRB_API int frb_attention_generic(const void* q, const void* k_pages, const void
     p.q = q; p.k_pages = k_pages; p.v_pages = v_pages; p.page_table = page_table; p.tok_pos = tok_pos;
     p.tok_slot = tok_slot; p.out = out; p.scale = scale; p.window = window; p.max_pages = max_pages;
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim; p.v_dim = v_dim; p.slopes = slopes;
-    p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_stride = gate_stride;
+    p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_stride = gate_stride; p.softcap = softcap;
     const int group = num_heads / num_kv_heads;
     const int nwarps = group < 8 ? group : 8;
     const size_t smem = ((size_t)KEY_BLOCK * (head_dim + 1) + (size_t)KEY_BLOCK * v_dim + (size_t)nwarps * head_dim) * sizeof(float);

@@ -6,10 +6,10 @@ FRB_API int frb_attention_decode_mma(const void* q, const void* k_pages, const v
                                      int max_pages, const int* seq_pos, const int* seq_slot, float* part_o, float* part_ml,
                                      void* out, int num_seqs, int num_heads, int num_kv_heads, int head_dim, float scale,
                                      int window, int max_chunks, int* status, const float* slopes, int chunk, const float* sinks,
-                                     cudaStream_t stream) {
+                                     float softcap, cudaStream_t stream) {
     return launch_attention_decode("attention_decode_mma", q, k_pages, v_pages, page_table, max_pages, seq_pos, seq_slot,
                                    part_o, part_ml, out, num_seqs, num_heads, num_kv_heads, head_dim, scale, window,
-                                   max_chunks, stream, status, slopes, chunk, sinks);
+                                   max_chunks, stream, status, slopes, chunk, sinks, softcap);
 }
 
 // ----------------------------------------------------------------------------- many tokens per sequence
@@ -31,6 +31,7 @@ struct PrefillAttnParams {
     const float* slopes;       // null, or one slope per query head: key j's score is lowered by slope * (position - j)
     int chunk;                 // 0, or a query sees only the keys of its own chunk of this many positions
     const float* sinks;        // null, or one number per query head whose exponential joins the softmax's denominator
+    float cap_scale, cap2;     // capped scores (capped_score2): scale / cap and cap * log2(e); cap2 0: none
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS <= 6 ? 2 : 1) attent
             __syncthreads();
             if (active) {
                 const SharedPage<HD> page = {stages + cur * 2 * TILE, stages + cur * 2 * TILE + TILE};
-                tile_page(st, page, page_index * FRB_PAGE, lo, hi, p.scale2, g, t, slope2);
+                tile_page(st, page, page_index * FRB_PAGE, lo, hi, p.scale2, g, t, slope2, p.cap_scale, p.cap2);
             }
             __syncthreads();                            // the stage is free for the page after the next
         }
@@ -130,7 +131,7 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
                                       int max_pages, const int* tile_seq, const int* tile_q0, int num_tiles,
                                       const int* seq_slot, const int* seq_start, const int* seq_q_len, const int* cu_q_len,
                                       void* out, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
-                                      const float* slopes, int chunk, const float* sinks, cudaStream_t stream) {
+                                      const float* slopes, int chunk, const float* sinks, float softcap, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0, "attention: %d heads over %d kv heads", num_heads, num_kv_heads);
     FRB_CHECK_ARG(head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128,
@@ -142,6 +143,7 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
     p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.scale2 = scale * 1.4426950408889634f; p.window = window;
     p.max_pages = max_pages; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.slopes = slopes;
     p.chunk = chunk; p.sinks = sinks;
+    p.cap_scale = softcap > 0.f ? scale / softcap : 0.f; p.cap2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     const int group = num_heads / num_kv_heads;
     const int nwarps = group < 8 ? group : 8;
     dim3 grid(num_tiles, num_kv_heads);

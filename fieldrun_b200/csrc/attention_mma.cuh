@@ -88,7 +88,8 @@ struct SharedPage {
 // of key j for the query at position hi[r] is lowered by slope * (hi[r] - j); 0 for none.
 template <int HD, typename Page>
 __device__ __forceinline__ void tile_page(RowTile<HD>& st, const Page& page, int key_base, const int (&lo)[2],
-                                          const int (&hi)[2], float scale2, int g, int t, float slope2 = 0.f) {
+                                          const int (&hi)[2], float scale2, int g, int t, float slope2 = 0.f,
+                                          float cap_scale = 0.f, float cap2 = 0.f) {
     float s[8][4];
     // scores: column block 4 m + u, column c = 2 t' + d of it stands for key 32 m + 8 t' + 2 u + d
 #pragma unroll
@@ -116,7 +117,9 @@ __device__ __forceinline__ void tile_page(RowTile<HD>& st, const Page& page, int
             for (int e = 0; e < 4; ++e) {
                 const int r = e >> 1;
                 const int key = key_base + 32 * m + 8 * t + 2 * u + (e & 1);
-                const float v = (key >= lo[r] && key <= hi[r]) ? fmaf(s[4 * m + u][e], scale2, slope2 * (float)(key - hi[r])) : -INFINITY;
+                const float raw = s[4 * m + u][e];
+                const float scaled = cap2 > 0.f ? capped_score2(raw, cap_scale, cap2) : raw * scale2;
+                const float v = (key >= lo[r] && key <= hi[r]) ? fmaf(slope2, (float)(key - hi[r]), scaled) : -INFINITY;
                 s[4 * m + u][e] = v;
                 mx[r] = fmaxf(mx[r], v);
             }
@@ -190,6 +193,7 @@ struct DecodeAttnParams {
     const float* slopes;       // null, or one slope per query head: key j's score is lowered by slope * (position - j)
     int chunk;                 // 0, or the token sees only the keys of its own chunk of this many positions
     const float* sinks;        // null, or one number per query head whose exponential joins the softmax's denominator
+    float cap_scale, cap2;     // capped scores (capped_score2): scale / cap and cap * log2(e); cap2 0: none
 };
 
 // The slopes of the two query heads that a thread's rows g and g + 8 of the group's tile stand for, times log2(e).
@@ -251,7 +255,8 @@ __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttn
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int key = key_base + 32 * m + 8 * t + 2 * u + (e & 1);
-                        const float v = (key >= lo_key && key <= hi_key) ? fmaf(acc[e], p.scale2, slope2[e >> 1] * (float)(key - hi_key)) : -INFINITY;
+                        const float scaled = p.cap2 > 0.f ? capped_score2(acc[e], p.cap_scale, p.cap2) : acc[e] * p.scale2;
+                        const float v = (key >= lo_key && key <= hi_key) ? fmaf(slope2[e >> 1], (float)(key - hi_key), scaled) : -INFINITY;
                         s[4 * m + u][e] = v;
                         row_max[e >> 1] = fmaxf(row_max[e >> 1], v);
                     }
@@ -398,7 +403,7 @@ static inline int launch_attention_decode(const char* what, const void* q, const
                                           float* part_o, float* part_ml, void* out, int num_seqs, int num_heads,
                                           int num_kv_heads, int head_dim, float scale, int window, int max_chunks,
                                           cudaStream_t stream, int* status = nullptr, const float* slopes = nullptr,
-                                          int chunk = 0, const float* sinks = nullptr) {
+                                          int chunk = 0, const float* sinks = nullptr, float softcap = 0.f) {
     if (num_seqs == 0) return 0;
     const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
@@ -412,6 +417,7 @@ static inline int launch_attention_decode(const char* what, const void* q, const
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks; p.status = status; p.slopes = slopes;
     p.chunk = chunk; p.sinks = sinks;
+    p.cap_scale = softcap > 0.f ? scale / softcap : 0.f; p.cap2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     dim3 grid(max_chunks, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
 #define FRB_LAUNCH_DECODE(HD)                                                       \
     launch_dependent(attention_decode_mma_kernel<HD>, dim3(grid), dim3(128), 0, stream, p);                   \

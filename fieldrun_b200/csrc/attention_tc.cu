@@ -88,13 +88,14 @@ struct AttnTcParams {
     const float* slopes;       // SLOPED kernels: one slope per query head; key j's score is lowered by slope * (i - j)
     int chunk;                 // 0, or a query sees only the keys of its own chunk of this many positions
     const float* sinks;        // null, or one number per query head whose exponential joins the softmax's denominator
+    float cap_scale, cap2;     // CAPPED kernels (capped_score2): scale / cap and cap * log2(e)
 };
 
 // grid (tile of 128 queries, head); the longest tiles of a sequence (its last ones) start first.
 // SLOPED: the scores carry a bias that falls with the distance between query and key (one more multiply-add on each
 // pair of scores; a page's maximum is then bounded from above by its largest score with the bias of its last key,
 // which is all the running maximum needs to be).
-template <int HD, bool SLOPED>
+template <int HD, bool SLOPED, bool CAPPED>
 __global__ void __launch_bounds__(AT_THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
@@ -244,6 +245,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < FRB_PAGE / 16; ++c) tmem_ld16(mine + 16 * c, raw[c]);
             tmem_wait_ld();
+            // CAPPED: every score becomes cap * tanh(score * scale / cap) * log2(e) first; what follows then sees a scale of one
+            const float scale2 = CAPPED ? 1.f : p.scale2;
+            if (CAPPED) {
+#pragma unroll
+                for (int c = 0; c < FRB_PAGE / 16; ++c)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        raw[c][i] = __float_as_uint(capped_score2(__uint_as_float(raw[c][i]), p.cap_scale, p.cap2));
+            }
             // Most pages lie wholly before the tile's first query (and inside the window): no key of theirs is
             // masked for any row of this warp, and the per-key comparisons are left out.
             const bool open_page = __all_sync(0xffffffffu, valid && key0 + FRB_PAGE - 1 <= hi && key0 >= lo);
@@ -256,7 +266,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                     for (int i = 0; i < 16; i += 2)
                         top[(i >> 1) & 3] = max3(top[(i >> 1) & 3], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
-                step_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * p.scale2;     // the scale is positive
+                step_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * scale2;     // the scale is positive
                 if (SLOPED) step_max += bias0 + slope2 * (float)(FRB_PAGE - 1);                // the bias grows with the key
             } else {
                 step_max = -INFINITY;
@@ -267,7 +277,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         const int key = key0 + 16 * c + i;
                         const float v = key >= lo && key <= hi ? __uint_as_float(raw[c][i]) : -INFINITY;
                         raw[c][i] = __float_as_uint(v);
-                        step_max = fmaxf(step_max, SLOPED ? fmaf(v, p.scale2, bias0 + slope2 * (float)(16 * c + i)) : v * p.scale2);
+                        step_max = fmaxf(step_max, SLOPED ? fmaf(v, scale2, bias0 + slope2 * (float)(16 * c + i)) : v * scale2);
                     }
             }
             float corr = 1.f;
@@ -278,7 +288,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // (a masked key gives 2^-inf = 0), one addition of the pair into one of four running pairs of sums.  (The
             // softmax is bound by the instructions it issues: a cubic on the multiply-add pipe for part of the
             // exponentials, to spare the special-function unit, made the kernel slower.)
-            const uint64_t scale_pair = pair_of(p.scale2, p.scale2), shift_pair = pair_of(bias0 - m_sub, bias0 - m_sub);
+            const uint64_t scale_pair = pair_of(scale2, scale2), shift_pair = pair_of(bias0 - m_sub, bias0 - m_sub);
             const uint64_t slope_pair = pair_of(slope2, slope2);
             uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};
             uint32_t packed[FRB_PAGE / 32][16];
@@ -391,7 +401,7 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
                                      int num_tiles, const int* seq_slot, const int* seq_start, const int* seq_q_len,
                                      const int* cu_q_len, void* out, int num_heads, int num_kv_heads, int head_dim, float scale,
                                      int window, int* status, const float* slopes, int chunk, const float* sinks,
-                                     cudaStream_t stream) {
+                                     float softcap, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     FRB_CHECK_ARG(head_dim == 64 || head_dim == 128, "tensor-core attention: head_dim %d is neither 64 nor 128", head_dim);
     FRB_CHECK_ARG(scale > 0.f, "tensor-core attention: a softmax scale of %g is not positive", (double)scale);
@@ -409,17 +419,19 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads; p.slopes = slopes;
     p.chunk = chunk; p.sinks = sinks;
+    p.cap_scale = softcap > 0.f ? scale / softcap : 0.f; p.cap2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    FRB_CHECK_ARG(!(softcap > 0.f && slopes), "tensor-core attention: capped scores together with distance slopes are not built");
     const size_t smem = (size_t)AT_QUERIES * head_dim * 2 + (size_t)AT_STAGES * AT_STEP_PAGES * 2 * FRB_PAGE * head_dim * 2 + 1024;
     dim3 grid(num_tiles, num_heads);
-#define FRB_LAUNCH_TC(HD, SLOPED)                                                                                            \
+#define FRB_LAUNCH_TC(HD, SLOPED, CAPPED)                                                                                    \
     do {                                                                                                                     \
-        cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SLOPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_dependent(attention_prefill_tc_kernel<HD, SLOPED>, grid, dim3(AT_THREADS), smem, stream, map_q, map_k, map_v, p); \
+        cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SLOPED, CAPPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_dependent(attention_prefill_tc_kernel<HD, SLOPED, CAPPED>, grid, dim3(AT_THREADS), smem, stream, map_q, map_k, map_v, p); \
     } while (0)
     if (head_dim == 128) {
-        if (slopes) FRB_LAUNCH_TC(128, true); else FRB_LAUNCH_TC(128, false);
+        if (slopes) FRB_LAUNCH_TC(128, true, false); else if (softcap > 0.f) FRB_LAUNCH_TC(128, false, true); else FRB_LAUNCH_TC(128, false, false);
     } else {
-        if (slopes) FRB_LAUNCH_TC(64, true); else FRB_LAUNCH_TC(64, false);
+        if (slopes) FRB_LAUNCH_TC(64, true, false); else if (softcap > 0.f) FRB_LAUNCH_TC(64, false, true); else FRB_LAUNCH_TC(64, false, false);
     }
 #undef FRB_LAUNCH_TC
     FRB_RETURN_LAUNCH("attention_prefill_tc");

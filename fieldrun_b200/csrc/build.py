@@ -29,13 +29,15 @@ class BuildError(RuntimeError):
 
 # Which sources make which library.  Every library also gets errors.cu (the error text of its entry points).
 GROUPS: dict[str, tuple[str, ...]] = {
-    "common": ("elementwise.cu", "layernorm.cu", "attention_generic.cu", "sampling.cu", "stream_ops.cu", "token_inputs.cu"),
+    "common": ("elementwise.cu", "layernorm.cu", "attention_generic.cu", "sampling.cu", "stream_ops.cu", "token_inputs.cu",
+               "sandwich_norm.cu"),
     "attention": ("attention_mma.cu", "attention_decode_tma.cu", "attention_tc.cu"),
     "streams": ("experts_stream.cu", "experts_mma.cu"),
     "experts": ("routing.cu", "experts_generic.cu"),
     "products": ("experts_tc.cu",),
     "recurrent": ("gla.cu",),
     "scans": ("scans.cu",),
+    "delta": ("delta_rule.cu",),
     "latent": ("latent_attention.cu", "latent_attention_tc.cu"),
     "extras": ("attention_decode_noalloc.cu", "wait_probe.cu"),
 }

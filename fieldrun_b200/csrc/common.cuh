@@ -103,6 +103,15 @@ __device__ __forceinline__ int first_visible_key(int pos, int window, int chunk)
     return lo;
 }
 
+// A capped attention score for kernels that keep scores as powers of two: raw * scale becomes cap * tanh(raw * scale / cap),
+// returned times log2(e).  cap_scale = scale / cap, cap2 = cap * log2(e).  tanh(x) = 1 - 2 / (exp(2x) + 1) with the
+// hardware's exponential and reciprocal (errors of a few 1e-7 of the cap: these kernels round the weights to bfloat16).
+__device__ __forceinline__ float capped_score2(float raw, float cap_scale, float cap2) {
+    const float x = fminf(raw * cap_scale, 40.f);
+    const float e = exp2f(x * 2.8853900817779268f);
+    return cap2 * (1.0f - __fdividef(2.0f, e + 1.0f));
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }

@@ -584,21 +584,30 @@ FRB_API int frb_add_rows(float* x, const float* delta, long long n, cudaStream_t
     FRB_RETURN_LAUNCH("add_rows");
 }
 
-// out[t, i] = silu(both[t, i]) * both[t, width + i], silu(x) = x / (1 + exp(-x))  (src/minimax.rs:31,119)
+// out[t, i] = act(both[t, i]) * both[t, width + i], act = silu(x) = x / (1 + exp(-x))  (src/minimax.rs:31,119) or, with
+// activation 1, the tanh form of gelu.  A row of `both` has `in_stride` floats; with row_gate >= 0 the row's output is
+// also multiplied by sigmoid(both[t, row_gate]): one number per row, for a unit whose output is gated per token.
 template <typename OutT>
-__global__ void gated_unit_kernel(const float* __restrict__ both, OutT* __restrict__ out, int width, size_t total) {
+__global__ void gated_unit_kernel(const float* __restrict__ both, int in_stride, OutT* __restrict__ out, int width, size_t total,
+                                  int activation, int row_gate) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / width, c = i - t * width;
-    const float g = both[t * 2 * width + c], u = both[t * 2 * width + width + c];
-    out[i] = from_f32<OutT>(g / (1.0f + expf(-g)) * u);
+    const float g = both[t * in_stride + c], u = both[t * in_stride + width + c];
+    float a = activation == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+    if (row_gate >= 0) a *= 1.0f / (1.0f + expf(-both[t * in_stride + row_gate]));
+    out[i] = from_f32<OutT>(a * u);
 }
 
-FRB_API int frb_gated_unit(const float* both, void* out, int out_dtype, int rows, int width, cudaStream_t stream) {
+FRB_API int frb_gated_unit(const float* both, int in_stride, void* out, int out_dtype, int rows, int width, int activation,
+                           int row_gate, cudaStream_t stream) {
     const size_t total = (size_t)rows * width;
     if (total == 0) return 0;
+    FRB_CHECK_ARG(in_stride >= 2 * width && row_gate < in_stride && (activation == 0 || activation == 1),
+                  "gated_unit: rows of %d floats for a width of %d, gate column %d, activation %d", in_stride, width, row_gate, activation);
     FRB_DISPATCH_DTYPE(out_dtype, OutT, {
-        gated_unit_kernel<OutT><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(both, (OutT*)out, width, total);
+        gated_unit_kernel<OutT><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(both, in_stride, (OutT*)out, width, total,
+                                                                                    activation, row_gate);
     });
     FRB_RETURN_LAUNCH("gated_unit");
 }

@@ -25,7 +25,7 @@ _SIGNATURES = {
     "frb_qkv_prepare": "pippifppipppipppiiiiiiiiiipifi",
     "frb_wait_probe": "lpp",
     "frb_add_rows": "ppl",
-    "frb_attention_generic": "pppipipppiiiifiipippi",
+    "frb_attention_generic": "pppipipppiiiifiipippif",
     "frb_layernorm": "ppppfppiii",
     "frb_unary_unit": "ppili",
     "frb_softcap": "plf",
@@ -48,10 +48,13 @@ _SIGNATURES = {
     "frb_sample_rows": "piipppp",
     "frb_argmax_rows": "piippp",
     "frb_sample_floor": "piippppppp",
-    "frb_gated_unit": "ppiii",
-    "frb_attention_decode_mma": "ppppipppppiiiifiippip",
-    "frb_attention_prefill_mma": "ppppippipppppiiifipip",
-    "frb_attention_decode_tma": "pppipipppppiiiifiiippip",
+    "frb_gated_unit": "pippiiii",
+    "frb_weighted_pair": "ppplff",
+    "frb_sandwich_norm": "pppffpppippfpfiipipi",
+    "frb_gated_delta_rule": "piiii" "piiii" "ppp" "ppp" "pll" "pi" "iiiii" "f",
+    "frb_attention_decode_mma": "ppppipppppiiiifiippipf",
+    "frb_attention_prefill_mma": "ppppippipppppiiifipipf",
+    "frb_attention_decode_tma": "pppipipppppiiiifiiippipf",
     "frb_expert_gemm_mma": "pppppppiipiiiiif",
     "frb_weight_stream": "pippppppiipiiiiiiipf",
     "frb_route_plan_small": "ppiiiifipppppppp",
@@ -59,7 +62,7 @@ _SIGNATURES = {
     "frb_router_logits": "ppiiip",
     "frb_expert_gemm_tc": "pipippppiipiiipif",
     "frb_gather_rows_bf16": "pppii",
-    "frb_attention_prefill_tc": "pippipippipppppiiifippip",
+    "frb_attention_prefill_tc": "pippipippipppppiiifippipf",
     "frb_embed_pair_rows": "pppipiiifillppppppi",
     "frb_token_side_gate": "pppipiiiiii",
     "frb_add_rms_normed": "pppiif",
@@ -84,7 +87,7 @@ _ENTRY_GROUPS = {
     "common": ("frb_embed_rows", "frb_rmsnorm", "frb_qkv_prepare", "frb_add_rows", "frb_attention_generic", "frb_layernorm",
                "frb_unary_unit", "frb_softcap", "frb_gated_unit", "frb_sample_rows", "frb_argmax_rows", "frb_sample_floor",
                "frb_dyt_norm", "frb_rms_blend", "frb_concat_rows", "frb_add_row_vector", "frb_head_gate", "frb_embed_pair_rows",
-               "frb_token_side_gate", "frb_add_rms_normed", "frb_add_typed_copy"),
+               "frb_token_side_gate", "frb_add_rms_normed", "frb_add_typed_copy", "frb_weighted_pair", "frb_sandwich_norm"),
     "latent": ("frb_latent_prepare", "frb_latent_queries", "frb_latent_attention", "frb_latent_gate",
                "frb_latent_attention_mma", "frb_latent_attention_tc"),
     "attention": ("frb_attention_decode_mma", "frb_attention_prefill_mma", "frb_attention_decode_tma", "frb_attention_prefill_tc"),
@@ -94,6 +97,7 @@ _ENTRY_GROUPS = {
     "products": ("frb_expert_gemm_tc", "frb_gather_rows_bf16"),
     "recurrent": ("frb_gla_scan",),
     "scans": ("frb_causal_conv", "frb_softplus_bias", "frb_selective_scan", "frb_gated_recurrence", "frb_state_space_scan", "frb_group_rms_norm"),
+    "delta": ("frb_gated_delta_rule",),
     "extras": ("frb_wait_probe",),
 }
 _GROUP_OF = {entry: group for group, entries in _ENTRY_GROUPS.items() for entry in entries}
@@ -602,8 +606,9 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: Optional[int], v_dim: Optional[int] = None,
                       slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
-    """``v_dim``: size of a value head if not ``head_dim``; ``slopes`` (float32 [num_heads]): the score of key j for
+                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                      softcap: Optional[float] = None) -> None:
+    """``softcap``: the scaled score s of every key becomes softcap * tanh(s / softcap); ``v_dim``: size of a value head if not ``head_dim``; ``slopes`` (float32 [num_heads]): the score of key j for
     the query at position i is lowered by slopes[h] * (i - j); ``chunk``: a query sees only the keys of its own chunk
     of that many positions; ``sinks`` (float32 [num_heads]): exp(sinks[h]) joins the softmax's denominator;
     ``gate`` (float32 [T, >= num_heads], rows may be wider): head h's output times sigmoid(gate[t, h])."""
@@ -622,11 +627,22 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     _call("frb_attention_generic", _ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q.dtype), _ptr(page_table),
           page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q.shape[0], num_heads, num_kv_heads, head_dim,
           float(scale), int(window or 0), int(v_dim or head_dim), _ptr(slopes), int(chunk or 0), _ptr(sinks), _ptr(gate),
-          gate.shape[1] if gate is not None else 0)
+          gate.shape[1] if gate is not None else 0, float(softcap or 0.0))
 
 
 ROUTE_SOFTMAX, ROUTE_FLOOR = 2, 4      # bits of the routing kernels' ``renormalize`` (bit 0: divide by the picked scores' sum)
 ROUTE_WEIGHT_FLOOR = 1e-20             # what bit 2 adds to that sum
+ROUTE_MAX_GROUPS, ROUTE_MAX_KEEP = 4095, 2047
+
+
+def route_groups(count: int, keep: int) -> int:
+    """The bits of ``renormalize`` that limit the choice to the ``keep`` best of ``count`` equal groups of neighbouring
+    experts (a group's value is its largest choice value); 0 when every group stays."""
+    if count <= 1 or keep >= count:
+        return 0
+    if count > ROUTE_MAX_GROUPS or not 1 <= keep <= ROUTE_MAX_KEEP:
+        raise KernelError(f"router: {keep} of {count} groups is more than the kernels take")
+    return (int(count) << 8) | (int(keep) << 20)
 
 
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renormalize: bool, routed_scale: float,
@@ -724,11 +740,84 @@ def sample_floor(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optiona
           _ptr(scratch[0]), _ptr(scratch[1]), _ptr(scratch[2]))
 
 
-def gated_unit(both: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(both[:, :w]) * both[:, w:]."""
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_unit(both: torch.Tensor, out: torch.Tensor, activation: str = "silu", row_gate: Optional[int] = None) -> None:
+    """out = act(both[:, :w]) * both[:, w:2w] with act silu or the tanh form of gelu; a row of ``both`` may be wider than
+    2w, and with ``row_gate`` (a column of ``both``) row t's output is also multiplied by sigmoid(both[t, row_gate])."""
     _want(both, torch.float32, "gate and up rows")
     rows, width = out.shape
-    _call("frb_gated_unit", _ptr(both), _ptr(out), _code(out.dtype), rows, width)
+    if activation not in GATED_ACTIVATIONS:
+        raise KernelError(f"gated_unit: activation {activation!r} is none of {sorted(GATED_ACTIVATIONS)}")
+    _call("frb_gated_unit", _ptr(both), both.shape[1], _ptr(out), _code(out.dtype), rows, width, GATED_ACTIVATIONS[activation],
+          -1 if row_gate is None else int(row_gate))
+
+
+def weighted_pair(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, ca: float, cb: float) -> None:
+    """out = ca * a + cb * b, float32."""
+    for t in (a, b, out):
+        _want(t, torch.float32, "weighted_pair's operands")
+    if a.shape != b.shape or a.shape != out.shape:
+        raise KernelError("weighted_pair: operands of unequal shapes")
+    _call("frb_weighted_pair", _ptr(a), _ptr(b), _ptr(out), out.numel(), float(ca), float(cb))
+
+
+def sandwich_norm(x: torch.Tensor, update_weight: torch.Tensor, update_eps: float, *, a: Optional[torch.Tensor] = None,
+                  b: Optional[torch.Tensor] = None, ca: float = 1.0, cb: float = 1.0,
+                  experts: Optional[tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None, rows: Optional[torch.Tensor] = None,
+                  weight: Optional[torch.Tensor] = None, eps: float = 0.0, out: Optional[torch.Tensor] = None,
+                  out32: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+    """u = ca * a + cb * b + the experts' weighted rows (rank order); x[src] + u / rms(u) * update_weight is stored back
+    into x when ``write_back``; ``out[r]`` = that sum / rms * weight with src = rows[r] (or r).  See sandwich_norm.cu."""
+    _want(x, torch.float32, "the residual stream")
+    _want(update_weight, torch.float32, "the update norm's weight")
+    for t in (a, b, out32, weight):
+        if t is not None:
+            _want(t, torch.float32, "sandwich_norm's float32 operands")
+    if rows is not None:
+        _want(rows, torch.int32, "row indices")
+    if out is not None and weight is None:
+        raise KernelError("sandwich_norm: a normed output needs the norm's weight")
+    y = ew = rowmap = None
+    top_k = 0
+    if experts is not None:
+        y, ew, rowmap = experts
+        _want(y, torch.float32, "expert outputs")
+        _want(ew, torch.float32, "expert weights")
+        _want(rowmap, torch.int32, "rows of the assignments")
+        top_k = ew.shape[-1]
+    num_rows = rows.numel() if rows is not None else x.shape[0]
+    _call("frb_sandwich_norm", _ptr(x), _ptr(a), _ptr(b), float(ca), float(cb), _ptr(y), _ptr(ew), _ptr(rowmap), top_k, _ptr(rows),
+          _ptr(update_weight), float(update_eps), _ptr(weight), float(eps), num_rows, x.shape[-1], _ptr(out),
+          _code(out.dtype) if out is not None else 0, _ptr(out32), int(write_back))
+
+
+def gated_delta_rule_takes(dim: int, vdim: int) -> bool:
+    """Whether :func:`gated_delta_rule` takes heads of ``dim`` keys and ``vdim`` values (delta_rule.cu's ``delta_shape``:
+    4, 8, 16 or 32 lanes a value column with up to 32 key rows each, lanes x values within a block of 1024 threads)."""
+    if dim < 1 or vdim < 1:
+        return False
+    for lanes in (4, 8, 16, 32):
+        if lanes * 32 < dim:
+            continue
+        return lanes * vdim <= 1024
+    return False
+
+
+def gated_delta_rule(conv: torch.Tensor, q_off: int, k_off: int, v_off: int, proj: torch.Tensor, b_off: int, a_off: int,
+                     g_off: int, a_log: torch.Tensor, dt_bias: torch.Tensor, norm: torch.Tensor, ctx, state: torch.Tensor,
+                     state_offset: int, out: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, eps: float) -> None:
+    """The gated delta rule over the step's new tokens (see delta_rule.cu): ``conv`` float32 [T, C] holds q, k, v behind
+    their convolution and silu at the three offsets, ``proj`` float32 [T, P] the logits of beta and of the decay (a number
+    per head each) and the output gate (heads * vdim) as projected; ``state`` [slots, 2, floats] with this recurrence's
+    [heads, dim, vdim] at ``state_offset``; ``out`` [T, heads * vdim] in the model dtype."""
+    for t in (conv, proj, a_log, dt_bias, norm):
+        _want(t, torch.float32, "gated_delta_rule's inputs")
+    _call("frb_gated_delta_rule", _ptr(conv), conv.shape[1], int(q_off), int(k_off), int(v_off), _ptr(proj), proj.shape[1],
+          int(b_off), int(a_off), int(g_off), _ptr(a_log), _ptr(dt_bias), _ptr(norm), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+          _ptr(ctx.cu_q_len), *_state_place(state, state_offset), _ptr(out), _code(out.dtype), ctx.num_seqs, int(heads),
+          int(kv_heads), int(dim), int(vdim), float(eps))
 
 
 MMA_HEAD_DIMS = (32, 64, 96, 128)
@@ -739,8 +828,10 @@ def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
                          seq_pos: torch.Tensor, seq_slot: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                          out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                          window: Optional[int], max_chunks: int, slopes: Optional[torch.Tensor] = None,
-                         chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> None:
+                         chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None,
+                         softcap: Optional[float] = None) -> None:
     """One token per sequence, bfloat16: keys split into chunks of 256 over blocks, merged in chunk order.
+    ``softcap`` (here and in the three kernels below): the scaled score s becomes softcap * tanh(s / softcap).
     ``slopes`` (float32 [num_heads], here and in the three kernels below): the score of key j for the query at
     position i is lowered by slopes[h] * (i - j); ``chunk``: a query sees only the keys of its own chunk of that many
     positions; ``sinks`` (float32 [num_heads]): exp(sinks[h]) joins the softmax's denominator."""
@@ -752,7 +843,7 @@ def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     _call("frb_attention_decode_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
           _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads, num_kv_heads,
           head_dim, float(scale), int(window or 0), max_chunks, _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0),
-          _ptr(sinks))
+          _ptr(sinks), float(softcap or 0.0))
 
 
 def _want_slopes(slopes: Optional[torch.Tensor], num_heads: int) -> None:
@@ -794,7 +885,7 @@ def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
                          out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                          window: Optional[int], max_chunks: int, chunks_per_block: Optional[int] = None,
                          slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                         sinks: Optional[torch.Tensor] = None) -> None:
+                         sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """As :func:`attention_decode_mma` for head sizes 64 and 128, with the pages copied into shared memory by
     TMA through a ring of stages, which keeps far more bytes in flight; a block takes ``chunks_per_block``
     chunks (default: :func:`decode_chunks_per_block`)."""
@@ -808,7 +899,7 @@ def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     _call("frb_attention_decode_tma", _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
           page_table.shape[1], _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads,
           num_kv_heads, head_dim, float(scale), int(window or 0), max_chunks, int(chunks_per_block),
-          _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0), _ptr(sinks))
+          _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0), _ptr(sinks), float(softcap or 0.0))
 
 
 def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
@@ -816,7 +907,7 @@ def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
                           seq_q_len: torch.Tensor, cu_q_len: torch.Tensor, out: torch.Tensor, *, num_heads: int,
                           num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                           slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                          sinks: Optional[torch.Tensor] = None) -> None:
+                          sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """Many tokens per sequence, bfloat16: tiles of 16 queries, causal, blockwise over the cache pages."""
     for t in (q, k_pages, v_pages, out):
         _want(t, torch.bfloat16, "tensor-core attention operands")
@@ -825,7 +916,7 @@ def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
     _call("frb_attention_prefill_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
           _ptr(tile_seq), _ptr(tile_q0), tile_seq.numel(), _ptr(seq_slot), _ptr(seq_start), _ptr(seq_q_len),
           _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), _ptr(slopes),
-          int(chunk or 0), _ptr(sinks))
+          int(chunk or 0), _ptr(sinks), float(softcap or 0.0))
 
 
 def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
@@ -1023,9 +1114,9 @@ def attention_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
                          seq_q_len: torch.Tensor, cu_q_len: torch.Tensor, out: torch.Tensor, *, num_heads: int,
                          num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                          slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                         sinks: Optional[torch.Tensor] = None) -> None:
+                         sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """Many tokens per sequence on tcgen05 tensor cores: tiles of 128 queries of one head (bfloat16, head sizes
-    64 and 128)."""
+    64 and 128).  Capped scores and distance slopes together are refused."""
     for t in (q, k_pages, v_pages, out):
         _want(t, torch.bfloat16, "tensor-core attention operands")
     _want_slopes(slopes, num_heads)
@@ -1033,7 +1124,7 @@ def attention_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     _call("frb_attention_prefill_tc", _ptr(q), q.shape[0], _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
           page_table.shape[1], _ptr(tile_seq), _ptr(tile_q0), tile_seq.numel(), _ptr(seq_slot), _ptr(seq_start),
           _ptr(seq_q_len), _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0),
-          _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0), _ptr(sinks))
+          _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0), _ptr(sinks), float(softcap or 0.0))
 
 
 def wait_probe(device, limit_cycles: int = 100_000) -> int:

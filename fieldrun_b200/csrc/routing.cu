@@ -18,6 +18,44 @@ __device__ __forceinline__ unsigned int ordered_bits(float v) {
 }
 
 enum { ROUTE_RENORMALIZE = 1, ROUTE_SOFTMAX = 2, ROUTE_FLOOR = 4 };
+// Experts in groups: bits 8..19 of `renormalize` hold the number of equal groups of neighbouring experts, bits 20..30 how
+// many groups stay.  A group's value is its largest choice value; only experts of the groups with the largest values
+// can be picked (ties between groups go to the lower group), the others' choice values count as minus infinity.
+#define ROUTE_GROUPS(flags) (((flags) >> 8) & 0xfff)
+#define ROUTE_KEEP(flags) (((flags) >> 20) & 0x7ff)
+
+// choice [E] (shared, this warp's) holds every expert's choice value; group_best [groups] is scratch.  Sets the choice
+// value of every expert outside the `keep` best groups to minus infinity.
+__device__ __forceinline__ void limit_to_groups(float* choice, float* group_best, int num_experts, int groups, int keep, int lane) {
+    const int size = num_experts / groups;
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+        float best = -INFINITY;
+        for (int e = g * size; e < (g + 1) * size; ++e) best = fmaxf(best, choice[e]);
+        group_best[g] = best;
+    }
+    __syncwarp();
+    for (int r = 0; r < keep; ++r) {
+        float best = -INFINITY;
+        int best_g = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32) {
+            const float c = group_best[g];
+            if (c != INFINITY && (best_g == 0x7fffffff || c > best)) { best = c; best_g = g; }     // kept groups are marked by +inf
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+            if (og != 0x7fffffff && (best_g == 0x7fffffff || ob > best || (ob == best && og < best_g))) { best = ob; best_g = og; }
+        }
+        __syncwarp();
+        if (lane == 0 && best_g != 0x7fffffff) group_best[best_g] = INFINITY;
+        __syncwarp();
+    }
+    for (int e = lane; e < num_experts; e += 32)
+        if (group_best[e / size] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+}
 
 #define PICK_PER_LANE 8      // experts a lane keeps in registers: up to 256 experts on the fast path
 
@@ -29,6 +67,8 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
                                              int* __restrict__ ids, float* __restrict__ weights, int lane) {
     const bool softmax = renormalize & ROUTE_SOFTMAX;
     float denom = (renormalize & ROUTE_FLOOR) ? 1e-20f : 0.f;
+    const int groups = ROUTE_GROUPS(renormalize), keep = ROUTE_KEEP(renormalize);
+    const bool grouped = groups > 1 && keep < groups;
     renormalize &= ROUTE_RENORMALIZE;
     if (num_experts <= 32 * PICK_PER_LANE && top_k <= 32) {
         // the lane's candidates stay in registers; NaN scores count as the smallest value
@@ -66,6 +106,15 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
                 sc[i] = 0.f;
                 mine[i] = -INFINITY;
             }
+        }
+        if (grouped) {                                  // through the warp's scratch: `score` is free here (the scores are in registers)
+#pragma unroll
+            for (int i = 0; i < PICK_PER_LANE; ++i)
+                if (lane + 32 * i < num_experts) choice[lane + 32 * i] = mine[i];
+            limit_to_groups(choice, score, num_experts, groups, keep, lane);
+#pragma unroll
+            for (int i = 0; i < PICK_PER_LANE; ++i)
+                if (lane + 32 * i < num_experts) mine[i] = choice[lane + 32 * i];
         }
         unsigned int taken = 0;                         // bit i: this lane's candidate i is handed out (or absent)
 #pragma unroll
@@ -110,10 +159,18 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
         for (int e = lane; e < num_experts; e += 32) total += expf(__ldcg(z + e) - top_logit);
         inv_total = 1.0f / warp_sum(total);
     }
+    if (grouped) {          // the choice values first: `score` is scratch for the groups' values before it holds the scores
+        for (int e = lane; e < num_experts; e += 32) {
+            const float s = softmax ? expf(__ldcg(z + e) - top_logit) * inv_total : 1.0f / (1.0f + expf(-__ldcg(z + e)));
+            const float c = bias ? s + bias[e] : s;
+            choice[e] = c == c ? c : -INFINITY;
+        }
+        limit_to_groups(choice, score, num_experts, groups, keep, lane);
+    }
     for (int e = lane; e < num_experts; e += 32) {
         const float s = softmax ? expf(__ldcg(z + e) - top_logit) * inv_total : 1.0f / (1.0f + expf(-__ldcg(z + e)));
         score[e] = s;
-        choice[e] = bias ? s + bias[e] : s;
+        if (!grouped) choice[e] = bias ? s + bias[e] : s;
     }
     __syncwarp();
     for (int r = 0; r < top_k; ++r) {

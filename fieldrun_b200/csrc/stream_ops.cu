@@ -175,3 +175,20 @@ FRB_API int frb_head_gate(void* out, int dtype, const float* gate, int stride, i
     });
     FRB_RETURN_LAUNCH("head_gate");
 }
+
+// ---------------------------------------------------------------------------------------------------- weighted_pair
+
+// out = ca * a + cb * b: two mixers' outputs side by side, each with a constant weight.
+__global__ void __launch_bounds__(ROW_BLOCK) weighted_pair_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                                  float* __restrict__ out, size_t total, float ca, float cb) {
+    after_previous_kernel();
+    const size_t i = (size_t)blockIdx.x * ROW_BLOCK + threadIdx.x;
+    if (i < total) out[i] = ca * a[i] + cb * b[i];
+}
+
+FRB_API int frb_weighted_pair(const float* a, const float* b, float* out, long long total, float ca, float cb, cudaStream_t stream) {
+    if (total == 0) return 0;
+    launch_dependent(weighted_pair_kernel, dim3((unsigned)((total + ROW_BLOCK - 1) / ROW_BLOCK)), dim3(ROW_BLOCK), 0, stream, a, b, out,
+                     (size_t)total, ca, cb);
+    FRB_RETURN_LAUNCH("weighted_pair");
+}

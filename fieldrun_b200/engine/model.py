@@ -47,7 +47,9 @@ class DecoderModel:
                 build_part("mixer", layer.mixer, self.dtype),
                 build_part("feed_forward", layer.feed_forward, self.dtype) if layer.feed_forward is not None else None,
                 build_part("norm", layer.mixer_norm, self.dtype),
-                build_part("norm", layer.feed_forward_norm, self.dtype) if layer.feed_forward_norm is not None else None))
+                build_part("norm", layer.feed_forward_norm, self.dtype) if layer.feed_forward_norm is not None else None,
+                build_part("norm", layer.mixer_out_norm, self.dtype) if layer.mixer_out_norm is not None else None,
+                build_part("norm", layer.feed_forward_out_norm, self.dtype) if layer.feed_forward_out_norm is not None else None))
         self.additions = [build_part("addition", layer.addition, self.dtype) if layer.addition is not None else None
                           for layer in plan.layers]
         self.connectors = [build_part("connector", spec, self.dtype) for spec in plan.connectors]

@@ -1,2 +1,2 @@
 """Built-in architectures; importing this package registers them."""
-from . import bamasun, depelix, fotanex, minimax_m2  # noqa: F401
+from . import bakasun, bamasun, depelix, fotanex, minimax_m2  # noqa: F401

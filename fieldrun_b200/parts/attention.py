@@ -20,7 +20,9 @@ line of an earlier layer, which the plan's run order names), ``chunk`` (the quer
 if floor(i / chunk) == floor(j / chunk), chunks counted from the sequence's position 0; the cache gives back the pages
 before the current chunk), ``sink`` (a learned number per query head whose exponential joins the softmax's
 denominator: no key, no value, not scaled, counted once), ``head_gate`` (head h's output is multiplied by
-sigmoid(W_g x)_h, one row of W_g per head, before the output projection).
+sigmoid(W_g x)_h, one row of W_g per head, before the output projection), ``sink_value`` (the sink as a constant for
+every head instead of a learned tensor: 0.0 adds one to the softmax's denominator), ``softcap`` (the scaled score s
+of every key becomes softcap * tanh(s / softcap) before the softmax).
 """
 from __future__ import annotations
 
@@ -73,6 +75,12 @@ class GQAAttention(Mixer):
         if self.chunk is not None and self.chunk <= 0:
             raise ValueError(f"attention in chunks of {self.chunk} positions")
         self.has_sink = bool(a.get("sink", False))
+        self.sink_value = float(a["sink_value"]) if a.get("sink_value") is not None else None
+        if self.has_sink and self.sink_value is not None:
+            raise ValueError("an attention sink is either a learned tensor (sink) or a constant (sink_value), not both")
+        self.softcap = float(a["softcap"]) if a.get("softcap") else None
+        if self.softcap is not None and not self.softcap > 0.0:
+            raise ValueError(f"a cap of {self.softcap} on the attention scores")
         self.has_head_gate = bool(a.get("head_gate", False))
         self.sinks: Optional[torch.Tensor] = None
         self.w_gate: Optional[torch.Tensor] = None
@@ -156,6 +164,8 @@ class GQAAttention(Mixer):
             self.cos, self.sin = self.position.shared_tables(num_positions, device)
         if self.slope_values is not None:
             self.slopes = torch.tensor(self.slope_values, dtype=torch.float64).to(torch.float32).to(device)
+        if self.sink_value is not None:
+            self.sinks = torch.full((self.num_heads,), self.sink_value, dtype=torch.float32, device=device)
 
     # -- one step --------------------------------------------------------------------------------------
     def forward(self, ctx, act: torch.Tensor, line: LineView, writes_cache: bool) -> torch.Tensor:
@@ -184,8 +194,10 @@ class GQAAttention(Mixer):
         All of them take the distance slopes, chunks and sinks; the general kernel applies the head gates itself, after
         the others a small kernel does."""
         common = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                      scale=self.softmax_scale, window=self.window, slopes=self.slopes, chunk=self.chunk, sinks=self.sinks)
-        if self.value_dim == self.head_dim and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
+                      scale=self.softmax_scale, window=self.window, slopes=self.slopes, chunk=self.chunk, sinks=self.sinks,
+                      softcap=self.softcap)
+        both = self.softcap is not None and self.slopes is not None     # the tcgen05 kernel has either, not both
+        if self.value_dim == self.head_dim and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS and not both:
             if ctx.is_decode and self.num_heads // self.num_kv_heads <= 16:
                 chunks = (ctx.max_kv_len + ops.ATTENTION_CHUNK - 1) // ops.ATTENTION_CHUNK
                 part_o = ctx.buffer("attention.part_o", (ctx.num_seqs, self.num_heads, chunks, self.head_dim), torch.float32)

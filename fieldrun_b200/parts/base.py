@@ -20,6 +20,8 @@ Interfaces
     ``pending`` is an update not yet added to x, so that the next norm adds it.
 ``Norm.add_normed(ctx, update, x)`` -> x in the model dtype
     the other place of a norm: x <- x + norm(update), for blocks whose sublayers read x itself.
+``Norm.normed(ctx, update)`` -> norm(update) in float32
+    a norm behind a sublayer whose block also has one in front (``NormedUpdate`` carries the pair to the next norm).
 ``Connector.forward(ctx, x, pending, first, index)`` -> the new stream [T, width] (float32)
     a part between two runs that rewrites the whole stream; ``first`` holds the embedding's rows.
 ``Addition.forward(ctx, x, pending)`` -> (x, pending)
@@ -127,6 +129,34 @@ class UpdateSum(DeferredUpdate):
         return total
 
 
+class WeightedPair(DeferredUpdate):
+    """Two float32 tensors [T, width] with a constant weight each, not yet summed: update = wa * a + wb * b.  A mixer
+    made of two mixers whose outputs are weighted by constants leaves them in this form, so that the norm which takes
+    the update can do the sum while it reads the rows."""
+
+    def __init__(self, a: torch.Tensor, b: torch.Tensor, wa: float, wb: float):
+        self.a, self.b, self.wa, self.wb = a, b, float(wa), float(wb)
+
+    def materialize(self, ctx) -> torch.Tensor:
+        from ..csrc import ops
+        out = ctx.buffer("weighted_pair.sum", tuple(self.a.shape), torch.float32)
+        ops.weighted_pair(self.a, self.b, out, self.wa, self.wb)
+        return out
+
+
+class NormedUpdate(DeferredUpdate):
+    """A sublayer's output that goes through a norm of its own before it is added to the stream (a block with a norm
+    behind each sublayer as well as in front of it): update = norm(inner), ``inner`` a float32 tensor or any deferred
+    form.  A norm that reads the stream next and knows the form norms ``inner``, adds and norms the sum in one pass;
+    any other norm gets the plain tensor from ``materialize``."""
+
+    def __init__(self, inner, norm: "Norm"):
+        self.inner, self.norm = inner, norm
+
+    def materialize(self, ctx) -> torch.Tensor:
+        return self.norm.normed(ctx, as_tensor(ctx, self.inner))
+
+
 def as_tensor(ctx, update):
     """The update as a float32 tensor, whatever form it came in (None stays None)."""
     return update.materialize(ctx) if isinstance(update, DeferredUpdate) else update
@@ -143,6 +173,10 @@ class Norm(Part):
         """For a block whose norm sits on the sublayer's output: x <- x + norm(update) in float32, in place;
         returns the new x in the model dtype (x itself in float32 mode), which the next sublayer reads."""
         raise NotImplementedError(f"norm {self.spec.kind!r} has no form that norms a sublayer's output")
+
+    def normed(self, ctx, update: torch.Tensor) -> torch.Tensor:
+        """norm(update) as a float32 tensor [T, width]: the norm of rows that are not the stream (a sublayer's output)."""
+        raise NotImplementedError(f"norm {self.spec.kind!r} has no form that norms rows other than the stream")
 
 
 class Position:
@@ -217,13 +251,17 @@ def shared_fetch(source: TensorSource, need: TensorNeed) -> torch.Tensor:
 
 
 class Block:
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm,
+                 mixer_out_norm: Optional[Norm] = None, feed_forward_out_norm: Optional[Norm] = None):
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        # norms behind the sublayers, for the arrangements that have them
+        self.mixer_out_norm, self.feed_forward_out_norm = mixer_out_norm, feed_forward_out_norm
 
     def parts(self) -> list[Part]:
-        """The block's parts; a layer without a feed-forward has neither it nor its norm."""
-        return [part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if part is not None]
+        """The block's parts; a layer without a feed-forward has neither it nor its norms."""
+        return [part for part in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward,
+                                  self.feed_forward_out_norm) if part is not None]
 
     def forward(self, ctx, x, pending, line: LineView, writes_cache: bool):
         raise NotImplementedError
@@ -281,5 +319,9 @@ def build_position(args: Optional[Mapping[str, Any]]) -> Optional[Position]:
     return position
 
 
-def build_block(kind: str, mixer, feed_forward, mixer_norm, feed_forward_norm) -> Block:
-    return _factory("block", kind)(mixer, feed_forward, mixer_norm, feed_forward_norm)
+def build_block(kind: str, mixer, feed_forward, mixer_norm, feed_forward_norm, mixer_out_norm=None,
+                feed_forward_out_norm=None) -> Block:
+    """``mixer_out_norm`` and ``feed_forward_out_norm``: the norms behind the sublayers, for a layer that names them."""
+    if mixer_out_norm is None and feed_forward_out_norm is None:
+        return _factory("block", kind)(mixer, feed_forward, mixer_norm, feed_forward_norm)
+    return _factory("block", kind)(mixer, feed_forward, mixer_norm, feed_forward_norm, mixer_out_norm, feed_forward_out_norm)

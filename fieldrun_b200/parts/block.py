@@ -2,12 +2,13 @@
 (the reference's two-norm pre-norm block, src/minimax.rs:261-284).  Each residual sum is
 left to the norm that follows it, which adds in float32 while it reads the stream.
 A second arrangement, ``output_norm``, has the norm behind the sublayer instead of in front of it; a third,
-``parallel_pre_norm``, runs the two sublayers side by side on the same x."""
+``parallel_pre_norm``, runs the two sublayers side by side on the same x; a fourth, ``sandwich_norm``, has a norm on
+both sides of each sublayer."""
 from __future__ import annotations
 
 import torch
 
-from .base import Block, UpdateSum, as_tensor, register_part
+from .base import Block, NormedUpdate, UpdateSum, as_tensor, register_part
 from .norm import LayerNorm
 
 
@@ -79,6 +80,24 @@ class ParallelPreNormBlock(Block):
         return x, UpdateSum([as_tensor(ctx, update), ff.forward_deferred(ctx, act2, act2_32)])
 
 
+class SandwichNormBlock(Block):
+    """A norm in front of and behind each sublayer: x <- x + norm1b(mixer(norm1(x))), then, if the layer has a
+    feed-forward, x <- x + norm2b(feed_forward(norm2(x))).  A sublayer's output is left with its norm
+    (``NormedUpdate``) for the norm that reads the stream next, which norms the output, adds it and norms the sum in
+    one pass."""
+
+    def forward(self, ctx, x, pending, line, writes_cache):
+        if self.mixer_out_norm is None or (self.feed_forward is not None and self.feed_forward_out_norm is None):
+            raise ValueError("a block with norms on both sides of its sublayers was given no norm for a sublayer's output")
+        act, _ = self.mixer_norm.forward(ctx, x, delta=pending)
+        pending = NormedUpdate(self.mixer.forward(ctx, act, line, writes_cache), self.mixer_out_norm)
+        if self.feed_forward is None:
+            return x, pending
+        act2, act2_32 = self.feed_forward_norm.forward(ctx, x, delta=pending, want32=self.feed_forward.wants_float32_input)
+        return x, NormedUpdate(self.feed_forward.forward_deferred(ctx, act2, act2_32), self.feed_forward_out_norm)
+
+
+register_part("block", "sandwich_norm", SandwichNormBlock, replace=True)
 register_part("block", "parallel_pre_norm", ParallelPreNormBlock, replace=True)
 register_part("block", "pre_norm", PreNormBlock, replace=True)
 register_part("block", "output_norm", OutputNormBlock, replace=True)

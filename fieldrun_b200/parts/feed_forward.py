@@ -14,6 +14,11 @@ Two more forms, each an argument: ``gate_limit`` > 0 makes an expert's unit the 
 u = clamp(x W3^T, -limit, limit), g sigmoid(1.702 g) (u + 1); ``weight_on_input`` puts an expert's weight on what goes
 in instead of on what comes out: the token's output is the sum of expert(w x) over its experts.  The rows are then
 scaled and sorted by a kernel of their own (product in float32, rounded once) and summed with weights of one.
+
+``groups`` ``{"count", "keep"}``: the experts form ``count`` equal groups of neighbours; a group's value is its largest
+choice value, and only experts of the ``keep`` groups with the largest values can be picked.  ``shared_expert``
+``{"width", "gate"}``: one more expert of the same form that every token uses; its output is added to the routed
+experts' sum, with ``gate`` multiplied by sigmoid(w_sg . x), one number per token.
 """
 from __future__ import annotations
 
@@ -23,7 +28,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import MATRIX, VECTOR, TensorNeed, TensorSource
-from .base import FeedForward, WeightedRows, register_part
+from .base import FeedForward, UpdateSum, WeightedRows, register_part
 from .linear import linear
 
 TILE_ROWS = 32        # rows of one expert that a block of the expert kernels takes
@@ -58,8 +63,23 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"a floor of {floor} under the sum of the picked scores: the kernels have 0 and {ops.ROUTE_WEIGHT_FLOOR}")
         # what the kernels take as their ``renormalize``: bit 0 divides by the sum of the picked scores, bit 1 makes the
         # scores a softmax over all experts (else sigmoids), bit 2 adds the floor to that sum
+        groups = a.get("groups") or {}
+        self.group_count, self.group_keep = int(groups.get("count", 1)), int(groups.get("keep", groups.get("count", 1)))
+        if self.group_count < 1 or not 1 <= self.group_keep <= self.group_count or int(a["num_experts"]) % self.group_count:
+            raise ValueError(f"{a['num_experts']} experts in {self.group_count} groups of which {self.group_keep} stay")
+        if self.group_keep * (int(a["num_experts"]) // self.group_count) < int(a["top_k"]):
+            raise ValueError(f"{self.group_keep} groups of {int(a['num_experts']) // self.group_count} experts hold fewer than the "
+                             f"{a['top_k']} experts a token picks")
+        # bits 8 and up: the groups (``ops.route_groups``)
         self.renormalize = (int(bool(a.get("renormalize", True))) | (ops.ROUTE_SOFTMAX if self.score == "softmax" else 0)
-                            | (ops.ROUTE_FLOOR if floor else 0))
+                            | (ops.ROUTE_FLOOR if floor else 0) | ops.route_groups(self.group_count, self.group_keep))
+        shared = a.get("shared_expert")
+        self.shared_width = int(shared["width"]) if shared else 0
+        self.shared_gate = bool(shared.get("gate", False)) if shared else False
+        if shared and self.shared_width < 1:
+            raise ValueError(f"a shared expert of width {self.shared_width}")
+        self.w_shared_in: Optional[torch.Tensor] = None       # gate rows, up rows, the token gate's row, zero rows up to a multiple of 16
+        self.w_shared_down: Optional[torch.Tensor] = None
         self.routed_scale = float(a.get("routed_scale", 1.0))
         self.gate_limit = float(a.get("gate_limit") or 0.0)
         if self.gate_limit < 0.0:
@@ -85,13 +105,24 @@ class RoutedExperts(FeedForward):
                 TensorNeed(self.name_of("w_up").format(e=e), (i, d), MATRIX, "normal"),
                 TensorNeed(self.name_of("w_down").format(e=e), (d, i), MATRIX, "normal"))
 
+    def _shared_needs(self) -> list[TensorNeed]:
+        if not self.shared_width:
+            return []
+        d, i = self.hidden_size, self.shared_width
+        needs = [TensorNeed(self.name_of("shared_gate"), (i, d), MATRIX, "normal"),
+                 TensorNeed(self.name_of("shared_up"), (i, d), MATRIX, "normal"),
+                 TensorNeed(self.name_of("shared_down"), (d, i), MATRIX, "normal")]
+        if self.shared_gate:
+            needs.append(TensorNeed(self.name_of("shared_token_gate"), (1, d), MATRIX, "normal"))
+        return needs
+
     def tensor_needs(self):
         needs = [TensorNeed(self.name_of("router"), (self.num_experts, self.hidden_size), VECTOR, "normal")]
         if self.choice_bias:
             needs.append(TensorNeed(self.name_of("choice_bias"), (self.num_experts,), VECTOR, "bias"))
         for e in range(self.num_experts):
             needs.extend(self._expert_needs(e))
-        return needs
+        return needs + self._shared_needs()
 
     def load(self, source: TensorSource) -> None:
         d, i, n = self.hidden_size, self.expert_width, self.num_experts
@@ -106,6 +137,24 @@ class RoutedExperts(FeedForward):
             self.w13[e, :i].copy_(gate)
             self.w13[e, i:].copy_(up)
             self.w2[e].copy_(down)
+        if self.shared_width:
+            fetched = [source.fetch(need) for need in self._shared_needs()]
+            width = self.shared_width
+            rows = -(-(2 * width + 1) // 16) * 16           # a product's features in steps of 16 (the streaming kernels' rule)
+            self.w_shared_in = torch.zeros((rows, d), dtype=fetched[0].dtype, device=fetched[0].device)
+            self.w_shared_in[:width].copy_(fetched[0])
+            self.w_shared_in[width:2 * width].copy_(fetched[1])
+            if self.shared_gate:
+                self.w_shared_in[2 * width].copy_(fetched[3].reshape(-1))
+            self.w_shared_down = fetched[2]
+
+    def shared(self, ctx, act: torch.Tensor) -> torch.Tensor:
+        """The shared expert's output [T, d] float32: silu(gate) * up, times the token's sigmoid gate where the part has one
+        (put on the hidden rows: the product behind it is linear), then the product out."""
+        both = linear(act, self.w_shared_in)
+        hidden = ctx.buffer("experts.shared_hidden", (act.shape[0], self.shared_width), self.dtype)
+        ops.gated_unit(both, hidden, "silu", row_gate=2 * self.shared_width if self.shared_gate else None)
+        return linear(hidden, self.w_shared_down)
 
     # -- one step --------------------------------------------------------------------------------------
     def logits(self, ctx, act32: torch.Tensor) -> torch.Tensor:
@@ -266,14 +315,19 @@ class RoutedExperts(FeedForward):
             y = self.experts(ctx, act, p, scaled)
             if self._ones is None or self._ones.shape[0] < weights.shape[0] or self._ones.device != weights.device:
                 self._ones = torch.ones((max(weights.shape[0], 1024), self.top_k), dtype=torch.float32, device=weights.device)
-            return WeightedRows(y, self._ones[:weights.shape[0]], p["row_of_assign"])
+            routed = WeightedRows(y, self._ones[:weights.shape[0]], p["row_of_assign"])
+            return UpdateSum([self.shared(ctx, act), routed]) if self.shared_width else routed
         y = self.experts(ctx, act, p)
         # each token's expert outputs, not yet summed: the norm after this layer adds them in rank order
-        return WeightedRows(y, weights, p["row_of_assign"])
+        routed = WeightedRows(y, weights, p["row_of_assign"])
+        if self.shared_width:
+            return UpdateSum([self.shared(ctx, act), routed])
+        return routed
 
 
 class DenseGatedUnit(FeedForward):
-    """silu(x W_gate^T) * (x W_up^T), then W_down: one expert's formula for every row (src/minimax.rs:116-120)."""
+    """act(x W_gate^T) * (x W_up^T), then W_down: one expert's formula for every row (src/minimax.rs:116-120), with
+    ``activation`` silu (the default) or gelu_tanh."""
 
     replayable = True
 
@@ -281,6 +335,9 @@ class DenseGatedUnit(FeedForward):
         super().__init__(spec, dtype)
         self.hidden_size = int(spec.args["hidden_size"])
         self.width = int(spec.args["width"])
+        self.activation = str(spec.args.get("activation", "silu"))
+        if self.activation not in ops.GATED_ACTIVATIONS:
+            raise ValueError(f"a gated unit with activation {self.activation!r}: known are {sorted(ops.GATED_ACTIVATIONS)}")
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
@@ -301,7 +358,7 @@ class DenseGatedUnit(FeedForward):
     def forward(self, ctx, act, act32):
         both = linear(act, self.w_gate_up)                         # float32 [T, 2I]
         hidden = ctx.buffer("dense.hidden", (act.shape[0], self.width), self.dtype)
-        ops.gated_unit(both, hidden)
+        ops.gated_unit(both, hidden, self.activation)
         return linear(hidden, self.w_down)
 
 

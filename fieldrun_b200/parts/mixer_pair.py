@@ -1,6 +1,8 @@
-"""Two mixers side by side on the same input: out = share * (left / rms(left) * w_left + right / rms(right) * w_right),
-each output divided by its root mean square over the model width (eps inside the root) and multiplied by a plain
-weight vector.  The two are parts of any registered kinds, given as ``PartSpec`` in the arguments ``left`` and
+"""Two mixers side by side on the same input.  ``blend: rms`` (the default): out = share * (left / rms(left) * w_left +
+right / rms(right) * w_right), each output divided by its root mean square over the model width (eps inside the root)
+and multiplied by a plain weight vector.  ``blend: weighted``: out = left_weight * left + right_weight * right with two
+constants and no tensors of its own; the two outputs are then left unsummed (``WeightedPair``) for the norm that takes
+the update.  The two are parts of any registered kinds, given as ``PartSpec`` in the arguments ``left`` and
 ``right``; they share the run's cache line, so at most one of them may keep keys and values and at most one a state."""
 from __future__ import annotations
 
@@ -11,7 +13,7 @@ import torch
 from ..cache import CacheNeed, LineView
 from ..csrc import ops
 from ..weights.loader import VECTOR, TensorNeed, TensorSource
-from .base import Mixer, as_tensor, build_part, register_part
+from .base import Mixer, WeightedPair, as_tensor, build_part, register_part
 
 
 class MixerPair(Mixer):
@@ -19,8 +21,12 @@ class MixerPair(Mixer):
         super().__init__(spec, dtype)
         a = spec.args
         self.hidden_size = int(a["hidden_size"])
-        self.eps = float(a["norm_eps"])
+        self.blend = a.get("blend", "rms")
+        if self.blend not in ("rms", "weighted"):
+            raise ValueError(f"a pair of mixers blended by {self.blend!r}: known are 'rms' and 'weighted'")
+        self.eps = float(a.get("norm_eps", 1e-6))
         self.share = float(a.get("share", 0.5))
+        self.left_weight, self.right_weight = float(a.get("left_weight", 1.0)), float(a.get("right_weight", 1.0))
         self.left: Mixer = build_part("mixer", a["left"], dtype)
         self.right: Mixer = build_part("mixer", a["right"], dtype)
         self.left_norm: Optional[torch.Tensor] = None
@@ -35,11 +41,14 @@ class MixerPair(Mixer):
         return [self.left, self.right]
 
     def tensor_needs(self):
+        if self.blend == "weighted":
+            return []
         return [TensorNeed(self.name_of("left_norm"), (self.hidden_size,), VECTOR, "around_one"),
                 TensorNeed(self.name_of("right_norm"), (self.hidden_size,), VECTOR, "around_one")]
 
     def load(self, source: TensorSource) -> None:
-        self.left_norm, self.right_norm = (source.fetch(need) for need in self.tensor_needs())
+        if self.blend == "rms":
+            self.left_norm, self.right_norm = (source.fetch(need) for need in self.tensor_needs())
         self.left.load(source)
         self.right.load(source)
 
@@ -60,6 +69,8 @@ class MixerPair(Mixer):
     def forward(self, ctx, act: torch.Tensor, line: LineView, writes_cache: bool) -> torch.Tensor:
         a = as_tensor(ctx, self.left.forward(ctx, act, line, writes_cache))
         b = as_tensor(ctx, self.right.forward(ctx, act, line, writes_cache))
+        if self.blend == "weighted":
+            return WeightedPair(a, b, self.left_weight, self.right_weight)
         out = ctx.buffer("mixer_pair.out", (act.shape[0], self.hidden_size), torch.float32)
         ops.rms_blend(a, b, self.left_norm, self.right_norm, out, self.eps, self.share)
         return out

@@ -1,15 +1,22 @@
 """RMSNorm: x * (1 / sqrt(mean(x^2) + eps)) * w per row, the weight used as it is
 (src/minimax.rs:56-66).  The kernel also performs the residual sum that precedes
-the norm, in float32, so the update of the stream and the norm read it once."""
+the norm, in float32, so the update of the stream and the norm read it once.
+``weight_offset`` (default 0) is added to the stored weight when it is loaded: a file that keeps the weight less one
+(stored around zero, used as 1 + w) gives 1.  The norm also serves behind a sublayer (``normed``, ``add_normed``), and
+an update that comes with such a norm (``NormedUpdate``) is normed, added and normed again in one kernel."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
 from ..csrc import ops
 from ..weights.loader import VECTOR, TensorNeed, TensorSource
-from .base import Norm, UpdateSum, WeightedRows, as_tensor, register_part
+from .base import Norm, NormedUpdate, UpdateSum, WeightedPair, WeightedRows, as_tensor, register_part
+
+# FIELDRUN_B200_FUSED_OUTPUT_NORM=0: an update with a norm of its own is normed and added by kernels of their own first
+FUSED_OUTPUT_NORM = os.environ.get("FIELDRUN_B200_FUSED_OUTPUT_NORM", "1") != "0"
 
 
 class RMSNorm(Norm):
@@ -19,17 +26,60 @@ class RMSNorm(Norm):
         super().__init__(spec, dtype)
         self.width = int(spec.args["width"])
         self.eps = float(spec.args["eps"])
+        self.weight_offset = float(spec.args.get("weight_offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_needs(self):
-        return [TensorNeed(self.name_of("weight"), (self.width,), VECTOR, "around_one")]
+        return [TensorNeed(self.name_of("weight"), (self.width,), VECTOR, "around_zero" if self.weight_offset else "around_one")]
 
     def load(self, source: TensorSource) -> None:
         self.weight = source.fetch(self.tensor_needs()[0])
+        if self.weight_offset:
+            self.weight = (self.weight.to(torch.float32) + self.weight_offset).contiguous()      # float32, rounded once
 
     accepts_deferred = True
 
+    def _parts_of(self, ctx, inner):
+        """(a, b, ca, cb, experts) of an update that the fused kernel sums itself; anything else as one tensor."""
+        if isinstance(inner, WeightedPair):
+            return inner.a, inner.b, inner.wa, inner.wb, None
+        if isinstance(inner, WeightedRows) and inner.top_k <= ops.NORM_MAX_SUMMED_ROWS:
+            return None, None, 1.0, 1.0, (inner.rows, inner.weights, inner.row_map)
+        if isinstance(inner, UpdateSum) and len(inner.tensors) <= 2 and all(w.top_k <= ops.NORM_MAX_SUMMED_ROWS for w in inner.weighted):
+            tensors = list(inner.tensors) + [None, None]
+            weighted = inner.weighted[0] if inner.weighted else None
+            return tensors[0], tensors[1], 1.0, 1.0, (weighted.rows, weighted.weights, weighted.row_map) if weighted else None
+        return as_tensor(ctx, inner), None, 1.0, 1.0, None
+
+    def normed(self, ctx, update):
+        out = ctx.buffer(f"norm.normed.{self.width}", tuple(update.shape), torch.float32)
+        out.zero_()
+        ops.add_rms_normed(out, update, self.weight, self.eps)
+        return out
+
+    def add_normed(self, ctx, update, x):
+        ops.add_rms_normed(x, as_tensor(ctx, update), self.weight, self.eps)
+        if self.dtype == torch.float32:
+            return x
+        act = ctx.buffer("stream.act", tuple(x.shape), self.dtype)
+        act.copy_(x)
+        return act
+
     def forward(self, ctx, x, *, delta=None, rows=None, want32=False, write_back=True):
+        if (isinstance(delta, NormedUpdate) and FUSED_OUTPUT_NORM and isinstance(delta.norm, RMSNorm)
+                and delta.norm.width == self.width and self.weight.dtype == torch.float32):
+            # the update's own norm, the sum and this norm in one pass over the row
+            a, b, ca, cb, experts = self._parts_of(ctx, delta.inner)
+            count = rows.numel() if rows is not None else x.shape[0]
+            out = ctx.buffer(f"norm.out.{self.width}", (count, self.width), self.dtype)
+            out32 = None
+            if want32:
+                out32 = out if self.dtype == torch.float32 else ctx.buffer(f"norm.out32.{self.width}", (count, self.width),
+                                                                           torch.float32)
+            ops.sandwich_norm(x, delta.norm.weight, delta.norm.eps, a=a, b=b, ca=ca, cb=cb, experts=experts, rows=rows,
+                              weight=self.weight, eps=self.eps, out=out, out32=None if out32 is out else out32,
+                              write_back=write_back)
+            return out, out32
         experts = None
         if isinstance(delta, WeightedRows) and delta.top_k <= ops.NORM_MAX_SUMMED_ROWS:
             experts, delta = (delta.rows, delta.weights, delta.row_map), None      # the kernel sums them as it reads x

@@ -10,6 +10,11 @@ convolution whose last inputs are part of the state too (kernels: scans.cu).
 ``scalar_decay_state_space`` (Mamba-2): [z | x | B | C | dt] = W_in h; [x | B | C] <- silu(conv(.)); dt <- softplus(dt + b);
     per head (head h uses group h // (heads / groups)):  S <- exp(-exp(A_log_h) dt) S + dt B x^T (S is [N, vdim]);
     y = S^T C + D_h x;  y * silu(z), then the root-mean-square norm in ``norm_groups`` equal parts times a weight, W_o.
+``gated_delta_rule``: q = W_q h, k = W_k h (``num_kv_heads`` x ``head_dim``), v = W_v h (``num_heads`` x ``value_dim``), each
+    through a convolution of its own and silu; q and k unit vectors per head, q also times head_dim^(-1/2); beta =
+    sigmoid(W_b h), g = exp(-exp(A_log_h) softplus(W_a h + dt_bias_h)), one of each per head; per head (head h uses q/k
+    head h // (heads / kv_heads)):  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q (S is [head_dim, value_dim]);
+    o / rms(o) * w (w [value_dim], shared by the heads) * silu(W_g h), then W_o.  Kernel: delta_rule.cu.
 
 The state of a slot lies in the cache line's state area as [2, floats] float32 (two copies, see scans.cu): the
 recurrence's state first, the convolution's last inputs behind it.  The projections are library products with
@@ -210,6 +215,75 @@ class ScalarDecayStateSpace(_StateMixer):
         return linear(out, w["o_proj"])
 
 
+class GatedDeltaRule(_StateMixer):
+    kernel_groups = ("common", "streams", "scans", "delta")
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        a = spec.args
+        self.hidden_size = int(a["hidden_size"])
+        self.num_heads, self.num_kv_heads = int(a["num_heads"]), int(a.get("num_kv_heads") or a["num_heads"])
+        self.head_dim, self.value_dim, self.taps = int(a["head_dim"]), int(a["value_dim"]), int(a["conv"])
+        self.norm_eps = float(a.get("norm_eps", 1e-6))
+        if min(self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.taps) < 1:
+            raise ValueError("a gated delta rule needs heads, kv heads, head_dim, value_dim and conv of at least 1")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} key heads")
+        if not ops.gated_delta_rule_takes(self.head_dim, self.value_dim):
+            raise ValueError(f"a state of {self.head_dim} x {self.value_dim} per head is more than the gated delta rule's kernel takes")
+        self.qk_width = self.num_kv_heads * self.head_dim
+        self.v_width = self.num_heads * self.value_dim
+        self.conv_channels = 2 * self.qk_width + self.v_width
+        self.state_floats = self.num_heads * self.head_dim * self.value_dim
+        self.conv_floats = (self.taps - 1) * self.conv_channels
+        # columns of the one product in: q | k | v | beta | decay | gate, then zero rows up to a multiple of 16
+        self.b_off = self.conv_channels
+        self.a_off = self.b_off + self.num_heads
+        self.g_off = self.a_off + self.num_heads
+        self.in_rows = -(-(self.g_off + self.v_width) // 16) * 16
+        self.w_in: Optional[torch.Tensor] = None
+        self.w: dict[str, torch.Tensor] = {}
+
+    def _needs(self) -> dict[str, TensorNeed]:
+        d, h = self.hidden_size, self.num_heads
+        return {
+            "q_proj": TensorNeed(self.name_of("q_proj"), (self.qk_width, d), MATRIX, "normal"),
+            "k_proj": TensorNeed(self.name_of("k_proj"), (self.qk_width, d), MATRIX, "normal"),
+            "v_proj": TensorNeed(self.name_of("v_proj"), (self.v_width, d), MATRIX, "normal"),
+            "beta_proj": TensorNeed(self.name_of("beta_proj"), (h, d), MATRIX, "normal"),
+            "decay_proj": TensorNeed(self.name_of("decay_proj"), (h, d), MATRIX, "normal"),
+            "gate_proj": TensorNeed(self.name_of("gate_proj"), (self.v_width, d), MATRIX, "normal"),
+            "q_conv": TensorNeed(self.name_of("q_conv"), (self.qk_width, self.taps), VECTOR, "around_half"),
+            "k_conv": TensorNeed(self.name_of("k_conv"), (self.qk_width, self.taps), VECTOR, "around_half"),
+            "v_conv": TensorNeed(self.name_of("v_conv"), (self.v_width, self.taps), VECTOR, "around_half"),
+            "a_log": TensorNeed(self.name_of("a_log"), (h,), VECTOR, "bias"),
+            "dt_bias": TensorNeed(self.name_of("dt_bias"), (h,), VECTOR, "bias"),
+            "norm": TensorNeed(self.name_of("norm"), (self.value_dim,), VECTOR, "around_one"),
+            "o_proj": TensorNeed(self.name_of("o_proj"), (d, self.v_width), MATRIX, "normal"),
+        }
+
+    def load(self, source: TensorSource) -> None:
+        w = self._fetch(source)
+        stacked = [w.pop(n) for n in ("q_proj", "k_proj", "v_proj", "beta_proj", "decay_proj", "gate_proj")]
+        self.w_in = torch.zeros((self.in_rows, self.hidden_size), dtype=stacked[0].dtype, device=stacked[0].device)
+        torch.cat(stacked, dim=0, out=self.w_in[:self.g_off + self.v_width])
+        w["conv"] = torch.cat([w.pop("q_conv"), w.pop("k_conv"), w.pop("v_conv")], dim=0).contiguous()
+        self.w = w
+
+    def forward(self, ctx, act: torch.Tensor, line: LineView, writes_cache: bool) -> torch.Tensor:
+        self._check(writes_cache)
+        w, rows = self.w, act.shape[0]
+        proj = linear(act, self.w_in)                                            # float32 [T, in_rows]: q | k | v | beta | decay | gate
+        qkv = ctx.buffer("delta_rule.qkv", (rows, self.conv_channels), torch.float32)
+        ops.causal_conv(proj, 0, self.conv_channels, w["conv"], None, ctx, line.state, self.state_floats, qkv, activation="silu")
+        out = ctx.buffer("delta_rule.out", (rows, self.v_width), self.dtype)
+        ops.gated_delta_rule(qkv, 0, self.qk_width, 2 * self.qk_width, proj, self.b_off, self.a_off, self.g_off, w["a_log"],
+                             w["dt_bias"], w["norm"], ctx, line.state, 0, out, heads=self.num_heads, kv_heads=self.num_kv_heads,
+                             dim=self.head_dim, vdim=self.value_dim, eps=self.norm_eps)
+        return linear(out, w["o_proj"])
+
+
+register_part("mixer", "gated_delta_rule", GatedDeltaRule, replace=True)
 register_part("mixer", "selective_scan", SelectiveScan, replace=True)
 register_part("mixer", "gated_linear_recurrence", GatedLinearRecurrence, replace=True)
 register_part("mixer", "scalar_decay_state_space", ScalarDecayStateSpace, replace=True)

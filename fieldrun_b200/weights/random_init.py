@@ -115,6 +115,8 @@ class RandomInit:
         key = tensor_key(self.seed, need.name)
         if need.init == "around_one":
             value = unit_normal(key, shape, device, self.norm_std).add_(self.norm_mean)
+        elif need.init == "around_zero":                         # a norm weight that is stored less one
+            value = unit_normal(key, shape, device, self.norm_std)
         elif need.init == "around_half":                         # a positive scale well inside a tanh's bend
             value = unit_normal(key, shape, device, 0.5 * self.norm_std).add_(0.5)
         elif need.init == "bias":
