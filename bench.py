@@ -122,7 +122,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out prefill and the batch 1/64 points")
     parser.add_argument("--skip-long-cache", action="store_true", help="leave out the batch of 8,192 to 65,536 tokens")
     parser.add_argument("--skip-loop", action="store_true", help="leave out the generate_batch timings")
-    parser.add_argument("--design", default=None, choices=["bamasun", "fotanex", "depelix"],
+    parser.add_argument("--design", default=None, choices=["bamasun", "fotanex", "depelix", "bakasun"],
                         help="instead of the default workload: this design beside MiniMax-M2 at equal sizes "
                              "(prompt and decode throughput, every kernel of a step); see fieldrun_b200/compare.py")
     parser.add_argument("--sizes", default="w2048,w4096", help="with --design: which of compare.SIZES, with commas between")

@@ -17,6 +17,10 @@ the same experts.  It measures
 layer before's latents, in turn; a hashed pair table on the embedding, a per-layer token input, routed experts with a
 clamped gate fed with weighted inputs) beside a MiniMax-M2 model with as many experts of the same size.
 
+``--design bakasun``: a Bakasun model (layers with a norm on both sides of each sublayer; twice windowed attention with
+a sink, then twice capped attention beside a gated delta rule, in turn; experts chosen among the best groups plus a
+gated shared expert) beside a MiniMax-M2 model with as many experts of the same size.
+
 The weights of every model are far larger than the L2 cache, and each timed step reads all of them.
 """
 from __future__ import annotations
@@ -105,6 +109,32 @@ def depelix_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, 
         listed.append({"type": "latent_attention" if turn in (1, 2) else "latent_attention_2", "mixer": mixer, "mlp": mlp})
     return {"architecture": "Depelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": 256},
             "embedding": {"bigram": {"buckets": 65536, "mul_prev": 1000003, "mul_cur": 7919}}, "layers": listed}
+
+
+# the Bakasun comparison: experts as in the two comparisons above, in four groups of which two stay; delta-rule heads of
+# 128 x 128 as published models with this recurrence have them
+BAKASUN_EXPERTS, BAKASUN_TOP, BAKASUN_FF_SHARE, BAKASUN_GROUPS, BAKASUN_KEEP = 16, 2, 4, 4, 2
+BAKASUN_WINDOW = 1024
+
+
+def bakasun_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, Any]:
+    """Layers in turns of four: twice attention with a window and a sink, twice capped attention beside a gated delta
+    rule; all with routed experts in groups and a shared expert of an expert's size."""
+    expert_ff = ff // BAKASUN_FF_SHARE // 128 * 128
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff},
+           "router": {"experts": BAKASUN_EXPERTS, "top": BAKASUN_TOP, "groups": {"count": BAKASUN_GROUPS, "keep": BAKASUN_KEEP}},
+           "shared": {"ff": expert_ff}}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": BAKASUN_WINDOW},
+                 "rot": {"base": 10000.0, "dims": dim // 2}}
+    left = dict(attention, softcap=30.0, rot={"base": 50000.0, "dims": dim // 2, "scaling": {"factor": 4.0}})
+    right = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4}
+    listed = []
+    for index in range(layers):
+        if index % 4 < 2:
+            listed.append({"type": "attention", "mixer": attention, "mlp": mlp})
+        else:
+            listed.append({"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}, "mlp": mlp})
+    return {"architecture": "Bakasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": listed}
 
 
 def minimax_config(width, heads, kv_heads, dim, ff, layers, vocab, experts=None) -> dict[str, Any]:
@@ -200,6 +230,9 @@ def compare_designs(sizes=("w2048", "w4096"), steps: int = 8, warmup: int = 3, d
         if design == "fotanex":
             experts = (FOTANEX_EXPERTS, FOTANEX_TOP, size["ff"] // FOTANEX_FF_SHARE // 128 * 128)
             pair = (("fotanex", fotanex_config(**size)), ("minimax_m2", minimax_config(**size, experts=experts)))
+        elif design == "bakasun":
+            experts = (BAKASUN_EXPERTS, BAKASUN_TOP, size["ff"] // BAKASUN_FF_SHARE // 128 * 128)
+            pair = (("bakasun", bakasun_config(**size)), ("minimax_m2", minimax_config(**size, experts=experts)))
         elif design == "depelix":
             experts = (DEPELIX_EXPERTS, DEPELIX_TOP, size["ff"] // DEPELIX_FF_SHARE // 128 * 128)
             pair = (("depelix", depelix_config(**size)), ("minimax_m2", minimax_config(**size, experts=experts)))

@@ -485,7 +485,60 @@ def scans(kind: str, launches: int) -> dict:
             "gbs": round(moved / ms / 1e6, 1)}
 
 
+def delta_rule(kind: str, launches: int) -> dict:
+    """The gated delta rule of delta_rule.cu alone, 16 heads of 128 x 128 over 4 key heads: ``prefill`` four prompts of
+    2,048 tokens, ``decode`` 64 sequences of one token.  Updates: state elements times tokens (four multiply-adds each)."""
+    heads, kv_heads, dim, vdim = 16, 4, 128, 128
+    lengths = [2048] * 4 if kind == "prefill" else [1] * 64
+    tokens = sum(lengths)
+    tables = _Tables(lengths)
+    channels = 2 * kv_heads * dim + heads * vdim
+    conv = torch.randn(tokens, channels, device=DEV)
+    proj = torch.randn(tokens, 2 * heads + heads * vdim, device=DEV)
+    a_log, dt_bias, norm = torch.zeros(heads, device=DEV), torch.zeros(heads, device=DEV), torch.ones(vdim, device=DEV)
+    state = torch.zeros(len(lengths), 2, heads * dim * vdim, device=DEV)
+    out = torch.empty(tokens, heads * vdim, dtype=torch.bfloat16, device=DEV)
+
+    def launch():
+        ops.gated_delta_rule(conv, 0, kv_heads * dim, 2 * kv_heads * dim, proj, 0, heads, 2 * heads, a_log, dt_bias, norm, tables,
+                             state, 0, out, heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, eps=1e-6)
+    ms = _time(launch, launches)
+    updates = tokens * heads * dim * vdim
+    moved = (conv.numel() + proj.numel()) * 4 + out.numel() * 2 + (2 * state[:, 0].numel() * 4 if kind == "decode" else 0)
+    return {"case": f"delta_rule_{kind}", "tokens": tokens, "ms": round(ms, 4), "updates_per_ns": round(updates / ms / 1e6, 1),
+            "tflops_float32": round(8.0 * updates / ms / 1e9, 2), "gbs": round(moved / ms / 1e6, 1)}
+
+
+def output_norm(launches: int, tokens: int) -> dict:
+    """The norm of a sublayer's output, the residual sum and the next norm in one pass (sandwich_norm.cu) at width 2048:
+    the update as two weighted tensors, and as a tensor plus two experts' rows a token; beside them the plain norm with the
+    sum (rmsnorm) of one tensor."""
+    width, top = 2048, 2
+    x = torch.randn(tokens, width, device=DEV)
+    a, b = torch.randn(tokens, width, device=DEV), torch.randn(tokens, width, device=DEV)
+    y = torch.randn(tokens * top, width, device=DEV)
+    ew = torch.rand(tokens, top, device=DEV)
+    rowmap = torch.randperm(tokens * top, device=DEV).to(torch.int32)
+    w = torch.ones(width, device=DEV)
+    out = torch.empty(tokens, width, dtype=torch.bfloat16, device=DEV)
+    out32 = torch.empty(tokens, width, device=DEV)
+    result = {"case": f"output_norm_{tokens}", "tokens": tokens}
+    for name, launch, floats in (
+            ("pair", lambda: ops.sandwich_norm(x, w, 1e-6, a=a, b=b, ca=0.6, cb=0.5, weight=w, eps=1e-6, out=out), 4 * width),
+            ("experts", lambda: ops.sandwich_norm(x, w, 1e-6, a=a, experts=(y, ew, rowmap), weight=w, eps=1e-6, out=out, out32=out32),
+             (6 + top) * width),
+            ("rmsnorm", lambda: ops.rmsnorm(x, w, 1e-6, out, delta=a, write_back=True), 3 * width)):
+        ms = _time(launch, launches)
+        result[name] = {"ms": round(ms, 4), "gbs": round(tokens * (floats * 4 + width * 2) / ms / 1e6, 1)}
+        x.normal_()
+    return result
+
+
 CASES = {
+    "delta_rule_prefill": lambda n: delta_rule("prefill", n),
+    "delta_rule_decode": lambda n: delta_rule("decode", n),
+    "output_norm_prefill": lambda n: output_norm(n, 8192),
+    "output_norm_decode": lambda n: output_norm(n, 8),
     "scan_selective": lambda n: scans("selective", n),
     "scan_state_space": lambda n: scans("state_space", n),
     "scan_gated": lambda n: scans("gated", n),
