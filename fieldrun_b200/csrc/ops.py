@@ -51,7 +51,7 @@ _SIGNATURES = {
     "frb_gated_unit": "pippiiii",
     "frb_weighted_pair": "ppplff",
     "frb_sandwich_norm": "pppffpppippfpfiipipi",
-    "frb_gated_delta_rule": "piiii" "piiii" "ppp" "ppp" "pll" "pi" "iiiii" "f",
+    "frb_gated_delta_rule": "piiii" "piiii" "ppp" "ppp" "pll" "pi" "pii" "iiiii" "f",
     "frb_attention_decode_mma": "ppppipppppiiiifiippipf",
     "frb_attention_prefill_mma": "ppppippipppppiiifipipf",
     "frb_attention_decode_tma": "pppipipppppiiiifiiippipf",
@@ -178,7 +178,7 @@ def _stream() -> int:
 
 
 _LAUNCHES = 0
-_KERNELS_PER_CALL = {"frb_gated_recurrence": 2, "frb_sample_floor": 3, "frb_argmax_rows": 2, "frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
+_KERNELS_PER_CALL = {"frb_gated_delta_rule": 2, "frb_gated_recurrence": 2, "frb_sample_floor": 3, "frb_argmax_rows": 2, "frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
 
 
 def launches() -> int:
@@ -795,29 +795,33 @@ def sandwich_norm(x: torch.Tensor, update_weight: torch.Tensor, update_eps: floa
 
 def gated_delta_rule_takes(dim: int, vdim: int) -> bool:
     """Whether :func:`gated_delta_rule` takes heads of ``dim`` keys and ``vdim`` values (delta_rule.cu's ``delta_shape``:
-    4, 8, 16 or 32 lanes a value column with up to 32 key rows each, lanes x values within a block of 1024 threads)."""
-    if dim < 1 or vdim < 1:
-        return False
-    for lanes in (4, 8, 16, 32):
-        if lanes * 32 < dim:
-            continue
-        return lanes * vdim <= 1024
-    return False
+    up to 32 lanes a value column with up to 32 key rows each; the value columns go over as many blocks as they need)."""
+    return 1 <= dim <= 1024 and vdim >= 1
 
 
 def gated_delta_rule(conv: torch.Tensor, q_off: int, k_off: int, v_off: int, proj: torch.Tensor, b_off: int, a_off: int,
                      g_off: int, a_log: torch.Tensor, dt_bias: torch.Tensor, norm: torch.Tensor, ctx, state: torch.Tensor,
-                     state_offset: int, out: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, eps: float) -> None:
+                     state_offset: int, out: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, eps: float,
+                     raw: Optional[torch.Tensor] = None, slices: Optional[int] = None) -> None:
     """The gated delta rule over the step's new tokens (see delta_rule.cu): ``conv`` float32 [T, C] holds q, k, v behind
     their convolution and silu at the three offsets, ``proj`` float32 [T, P] the logits of beta and of the decay (a number
     per head each) and the output gate (heads * vdim) as projected; ``state`` [slots, 2, floats] with this recurrence's
-    [heads, dim, vdim] at ``state_offset``; ``out`` [T, heads * vdim] in the model dtype."""
+    [heads, dim, vdim] at ``state_offset``; ``out`` [T, heads * vdim] in the model dtype.  ``raw`` (float32, as many
+    elements as ``out``): with it the kernel may cut every head's value columns into slices over blocks (``slices``: how
+    many; default: as the sizes and the step's number of sequences want it); a token's output has the same bits however
+    they are cut.  Without it, heads too wide for one block are refused."""
     for t in (conv, proj, a_log, dt_bias, norm):
         _want(t, torch.float32, "gated_delta_rule's inputs")
+    if raw is None:
+        slices = 1
+    else:
+        _want(raw, torch.float32, "the unnormed outputs")
+        if raw.numel() < out.numel():
+            raise KernelError("gated_delta_rule: the buffer of unnormed outputs is smaller than the outputs")
     _call("frb_gated_delta_rule", _ptr(conv), conv.shape[1], int(q_off), int(k_off), int(v_off), _ptr(proj), proj.shape[1],
           int(b_off), int(a_off), int(g_off), _ptr(a_log), _ptr(dt_bias), _ptr(norm), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
-          _ptr(ctx.cu_q_len), *_state_place(state, state_offset), _ptr(out), _code(out.dtype), ctx.num_seqs, int(heads),
-          int(kv_heads), int(dim), int(vdim), float(eps))
+          _ptr(ctx.cu_q_len), *_state_place(state, state_offset), _ptr(out), _code(out.dtype), _ptr(raw), conv.shape[0], int(slices or 0),
+          ctx.num_seqs, int(heads), int(kv_heads), int(dim), int(vdim), float(eps))
 
 
 MMA_HEAD_DIMS = (32, 64, 96, 128)

@@ -7,10 +7,12 @@
 //
 // All in float32; `out` is rounded to the model's type (and given in float32 as well when `out32` is set).  One block
 // per output row r, src = rows ? rows[r] : r.  The row stays in shared memory between the two statistics, so the
-// stream is read once and written once.  The order of every sum is fixed by the block's size alone.
+// stream is read once and written once.  The order of every sum is fixed by the block's size, which follows the number
+// of rows in the step (as the plain norm's does).
 #include "common.cuh"
 
-#define SANDWICH_BLOCK 256
+// A step of few rows takes blocks of 1024 threads (the row's latency is the step's), a step of many rows blocks of 256.
+#define SANDWICH_FEW_ROWS 64
 #define SANDWICH_MAX_TOP_K 32
 
 struct SandwichParams {
@@ -29,7 +31,7 @@ struct SandwichParams {
     int top_k, width, write_back;
 };
 
-template <typename OutT>
+template <typename OutT, int SANDWICH_BLOCK>
 __global__ void __launch_bounds__(SANDWICH_BLOCK) sandwich_norm_kernel(SandwichParams p) {
     extern __shared__ __align__(16) float row[];         // [width]: u, then v
     __shared__ float scratch[32];
@@ -94,9 +96,15 @@ FRB_API int frb_sandwich_norm(float* x, const float* a, const float* b, float ca
     p.out = out; p.out32 = out32; p.ca = ca; p.cb = cb; p.eps_u = eps_u; p.eps = eps; p.top_k = top_k; p.width = width;
     p.write_back = write_back;
     FRB_DISPATCH_DTYPE(out_dtype, OutT, {
-        auto kernel = sandwich_norm_kernel<OutT>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_dependent(kernel, dim3(num_rows), dim3(SANDWICH_BLOCK), smem, stream, p);
+        if (num_rows <= SANDWICH_FEW_ROWS && width >= 1024) {
+            auto kernel = sandwich_norm_kernel<OutT, 1024>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch_dependent(kernel, dim3(num_rows), dim3(1024), smem, stream, p);
+        } else {
+            auto kernel = sandwich_norm_kernel<OutT, 256>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch_dependent(kernel, dim3(num_rows), dim3(256), smem, stream, p);
+        }
     });
     FRB_RETURN_LAUNCH("sandwich_norm");
 }

@@ -277,9 +277,10 @@ class GatedDeltaRule(_StateMixer):
         qkv = ctx.buffer("delta_rule.qkv", (rows, self.conv_channels), torch.float32)
         ops.causal_conv(proj, 0, self.conv_channels, w["conv"], None, ctx, line.state, self.state_floats, qkv, activation="silu")
         out = ctx.buffer("delta_rule.out", (rows, self.v_width), self.dtype)
+        raw = ctx.buffer("delta_rule.raw", (rows, self.v_width), torch.float32)      # for steps that cut the heads over blocks
         ops.gated_delta_rule(qkv, 0, self.qk_width, 2 * self.qk_width, proj, self.b_off, self.a_off, self.g_off, w["a_log"],
                              w["dt_bias"], w["norm"], ctx, line.state, 0, out, heads=self.num_heads, kv_heads=self.num_kv_heads,
-                             dim=self.head_dim, vdim=self.value_dim, eps=self.norm_eps)
+                             dim=self.head_dim, vdim=self.value_dim, eps=self.norm_eps, raw=raw)
         return linear(out, w["o_proj"])
 
 

@@ -487,9 +487,9 @@ def scans(kind: str, launches: int) -> dict:
 
 def delta_rule(kind: str, launches: int) -> dict:
     """The gated delta rule of delta_rule.cu alone, 16 heads of 128 x 128 over 4 key heads: ``prefill`` four prompts of
-    2,048 tokens, ``decode`` 64 sequences of one token.  Updates: state elements times tokens (four multiply-adds each)."""
+    2,048 tokens (``prefill_whole``: every head's value columns in one block), ``decode`` 64 sequences of one token.  Updates: state elements times tokens (four multiply-adds each)."""
     heads, kv_heads, dim, vdim = 16, 4, 128, 128
-    lengths = [2048] * 4 if kind == "prefill" else [1] * 64
+    lengths = [2048] * 4 if kind.startswith("prefill") else [1] * 64
     tokens = sum(lengths)
     tables = _Tables(lengths)
     channels = 2 * kv_heads * dim + heads * vdim
@@ -498,10 +498,12 @@ def delta_rule(kind: str, launches: int) -> dict:
     a_log, dt_bias, norm = torch.zeros(heads, device=DEV), torch.zeros(heads, device=DEV), torch.ones(vdim, device=DEV)
     state = torch.zeros(len(lengths), 2, heads * dim * vdim, device=DEV)
     out = torch.empty(tokens, heads * vdim, dtype=torch.bfloat16, device=DEV)
+    raw = torch.empty(tokens, heads * vdim, device=DEV)
+    slices = None if kind != "prefill_whole" else 1
 
     def launch():
         ops.gated_delta_rule(conv, 0, kv_heads * dim, 2 * kv_heads * dim, proj, 0, heads, 2 * heads, a_log, dt_bias, norm, tables,
-                             state, 0, out, heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, eps=1e-6)
+                             state, 0, out, heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, eps=1e-6, raw=raw, slices=slices)
     ms = _time(launch, launches)
     updates = tokens * heads * dim * vdim
     moved = (conv.numel() + proj.numel()) * 4 + out.numel() * 2 + (2 * state[:, 0].numel() * 4 if kind == "decode" else 0)
@@ -536,6 +538,7 @@ def output_norm(launches: int, tokens: int) -> dict:
 
 CASES = {
     "delta_rule_prefill": lambda n: delta_rule("prefill", n),
+    "delta_rule_prefill_whole": lambda n: delta_rule("prefill_whole", n),
     "delta_rule_decode": lambda n: delta_rule("decode", n),
     "output_norm_prefill": lambda n: output_norm(n, 8192),
     "output_norm_decode": lambda n: output_norm(n, 8),

@@ -211,11 +211,12 @@ def delta_plain(conv, proj, a_log, dt_bias, norm, heads, kv_heads, dim, vdim, ep
     return (o * pb.silu(p[:, 5 + 2 * heads:].reshape(rows, heads, vdim))).reshape(rows, heads * vdim)
 
 
-def run_delta(conv, proj, a_log, dt_bias, norm, tables, state, offset, heads, kv_heads, dim, vdim, eps, dtype="float32"):
+def run_delta(conv, proj, a_log, dt_bias, norm, tables, state, offset, heads, kv_heads, dim, vdim, eps, dtype="float32", slices=None):
     out = torch.empty((conv.shape[0], heads * vdim), dtype=TORCH[dtype], device=DEV)
+    raw = torch.full((conv.shape[0], heads * vdim), float("nan"), dtype=torch.float32, device=DEV)
     ops().gated_delta_rule(f32(conv), 3, 3 + kv_heads * dim, 3 + 2 * kv_heads * dim, f32(proj), 5, 5 + heads, 5 + 2 * heads,
                            f32(a_log), f32(dt_bias), f32(norm), tables, state, offset, out, heads=heads, kv_heads=kv_heads, dim=dim,
-                           vdim=vdim, eps=eps)
+                           vdim=vdim, eps=eps, raw=raw, slices=slices)
     return f64(out)
 
 
@@ -244,6 +245,17 @@ def test_gated_delta_rule_carries_its_state_through_portions_and_reused_slots(he
                 got[b].append(out[lo:hi])
         for b in range(len(lengths)):
             close(np.concatenate(got[b]), want[b], 3e-5, f"turn {turn}, sequence {b}")
+    # a head's value columns cut over 1, 2, 3 and 7 blocks: the same bits
+    conv, proj = np.concatenate([c for c, _ in inputs]), np.concatenate([p for _, p in inputs])
+    results = []
+    for slices in (1, 2, 3, 7):
+        state.zero_()
+        results.append(run_delta(conv, proj, a_log, dt_bias, norm, Tables(slots, [0] * 4, lengths), state, offset, heads, kv_heads, dim, vdim,
+                                 1e-5, slices=slices))
+        if slices > 1:
+            assert np.array_equal(results[0], results[-1]), f"{slices} slices"
+            assert torch.equal(state, kept), f"the state after {slices} slices"
+        kept = state.clone()
 
 
 def test_gated_delta_rule_remembers_a_token_hundreds_of_steps_back():
