@@ -92,18 +92,31 @@ __global__ void __launch_bounds__(512) gated_delta_rule_kernel(DeltaParams p) {
         float* in_gate = in_v + DELTA_TOKENS * cols;
         float* in_ba = in_gate + DELTA_TOKENS * cols;
         const int t0 = n * DELTA_TOKENS, count = min(DELTA_TOKENS, n_tok - t0);
-        for (int i = threadIdx.x; i < count * dim; i += blockDim.x) {
-            const int t = i / dim, d = i - t * dim;
-            const float* row = p.conv + (size_t)(row0 + t0 + t) * p.conv_stride + kvh * dim + d;
-            delta_copy_async4(in_q + i, row + p.q_off);
-            delta_copy_async4(in_k + i, row + p.k_off);
+        // (token, entry) of this thread's copies step by step, without a division a copy
+        {
+            int t = threadIdx.x / dim, d = threadIdx.x - t * dim;
+            const int step_t = blockDim.x / dim, step_d = blockDim.x - step_t * dim;
+            for (int i = threadIdx.x; i < count * dim; i += blockDim.x) {
+                const float* row = p.conv + (size_t)(row0 + t0 + t) * p.conv_stride + kvh * dim + d;
+                delta_copy_async4(in_q + i, row + p.q_off);
+                delta_copy_async4(in_k + i, row + p.k_off);
+                t += step_t;
+                d += step_d;
+                if (d >= dim) { d -= dim; ++t; }
+            }
         }
-        for (int i = threadIdx.x; i < count * cols; i += blockDim.x) {
-            const int t = i / cols, d = i - t * cols;
-            if (col0 + d < vdim) {
-                const size_t row = (size_t)(row0 + t0 + t);
-                delta_copy_async4(in_v + i, p.conv + row * p.conv_stride + p.v_off + h * vdim + col0 + d);
-                if (fused) delta_copy_async4(in_gate + i, p.proj + row * p.proj_stride + p.g_off + h * vdim + col0 + d);
+        {
+            int t = threadIdx.x / cols, d = threadIdx.x - t * cols;
+            const int step_t = blockDim.x / cols, step_d = blockDim.x - step_t * cols;
+            for (int i = threadIdx.x; i < count * cols; i += blockDim.x) {
+                if (col0 + d < vdim) {
+                    const size_t row = (size_t)(row0 + t0 + t);
+                    delta_copy_async4(in_v + i, p.conv + row * p.conv_stride + p.v_off + h * vdim + col0 + d);
+                    if (fused) delta_copy_async4(in_gate + i, p.proj + row * p.proj_stride + p.g_off + h * vdim + col0 + d);
+                }
+                t += step_t;
+                d += step_d;
+                if (d >= cols) { d -= cols; ++t; }
             }
         }
         if (threadIdx.x < 2 * count) {
@@ -185,11 +198,15 @@ __global__ void __launch_bounds__(512) gated_delta_rule_kernel(DeltaParams p) {
                     sq[c] = fmaf(S[4 * i + 2][c], qq.z, sq[c]); sq[c] = fmaf(S[4 * i + 3][c], qq.w, sq[c]);
                 }
             }
-            for (int o = 1; o < P; o <<= 1) {
 #pragma unroll
-                for (int c = 0; c < C; ++c) {
-                    sk[c] += __shfl_xor_sync(0xffffffffu, sk[c], o);
-                    sq[c] += __shfl_xor_sync(0xffffffffu, sq[c], o);
+            for (int round = 0; round < 5; ++round) {          // P is the same for the whole block: no branch diverges
+                const int o = 1 << round;
+                if (o < P) {
+#pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        sk[c] += __shfl_xor_sync(0xffffffffu, sk[c], o);
+                        sq[c] += __shfl_xor_sync(0xffffffffu, sq[c], o);
+                    }
                 }
             }
             // the decay is kept as g - 1 and applied as S + (g - 1) S: rounded to float32, a decay close to one would lose
@@ -274,7 +291,7 @@ __global__ void __launch_bounds__(128) delta_output_kernel(DeltaParams p, int nu
 }
 
 // How a head's state is shared out: `lanes` (a power of two up to 32) neighbouring lanes take `columns` neighbouring value
-// columns, each lane `rows` (4, 8, 16 or 32) key rows of them.  `many_warps`: up to eight rows of one column a thread;
+// columns, each lane `rows` (4, 8, 16 or 32) key rows of them.  `many_warps`: up to eight rows of two columns a thread;
 // else up to 64 state elements a thread (four columns of up to 16 rows; two of 32).  0 lanes: more keys than 32 lanes of
 // 32 rows hold.
 static long frb_dependent_launch_blocks_or_sms() {
@@ -293,7 +310,7 @@ static void delta_shape(int dim, bool many_warps, int& lanes, int& rows, int& co
     while (lanes < 32 && (dim + lanes - 1) / lanes > most) lanes *= 2;
     const int need = (dim + lanes - 1) / lanes;
     rows = need <= 4 ? 4 : need <= 8 ? 8 : need <= 16 ? 16 : 32;
-    columns = rows == 32 ? 2 : (many_warps && rows <= 8) ? 1 : 4;
+    columns = rows == 32 ? 2 : (many_warps && rows <= 8) ? 2 : 4;
     if (dim < 1 || need > 32) lanes = 0;
 }
 
@@ -308,9 +325,11 @@ FRB_API int frb_gated_delta_rule(const float* conv, int conv_stride, int q_off, 
     FRB_CHECK_ARG(heads <= 65535, "gated delta rule: %d heads exceed the grid", heads);
     int lanes, rows, columns;
     // A prompt's tokens go one after the other through every thread of their head, and what hides one thread's latencies
-    // is other warps: eight rows of one column a thread, sixteen warps a block.  A step of single tokens is bound by the
+    // is other warps: eight rows of two columns a thread, sixteen warps a block.  A step of single tokens is bound by the
     // state it reads and writes: up to 64 elements a thread, fewer loads of k and q from shared memory.  (Measured on a
-    // B200, 16 heads of 128 x 128: four prompts of 2,048 tokens 1.78 against 2.64 ms, 64 single tokens 0.153 against 0.072.)
+    // B200, 16 heads of 128 x 128, four prompts of 2,048 tokens: eight rows of one, two, four columns a thread 1.69, 1.40,
+    // 1.98 ms, sixteen rows of four columns 2.64; 64 single tokens: 0.153 with eight rows of one column, 0.072 with sixteen
+    // of four.)
     const bool prompt = num_rows > num_seqs;
     delta_shape(dim, prompt, lanes, rows, columns);
     FRB_CHECK_ARG(vdim >= 1 && lanes > 0, "gated delta rule: heads of %d keys and %d values (the kernel takes up to 1024 keys)", dim, vdim);
@@ -355,8 +374,8 @@ FRB_API int frb_gated_delta_rule(const float* conv, int conv_stride, int q_off, 
         launch_dependent(kernel, grid, dim3(threads), smem, stream, p);                                              \
     } while (0)
     FRB_DISPATCH_DTYPE(out_dtype, OutT, {
-        if (rows == 4 && columns == 1) FRB_LAUNCH_DELTA(4, 1);
-        else if (rows == 8 && columns == 1) FRB_LAUNCH_DELTA(8, 1);
+        if (rows == 4 && columns == 2) FRB_LAUNCH_DELTA(4, 2);
+        else if (rows == 8 && columns == 2) FRB_LAUNCH_DELTA(8, 2);
         else if (rows == 4) FRB_LAUNCH_DELTA(4, 4);
         else if (rows == 8) FRB_LAUNCH_DELTA(8, 4);
         else if (rows == 16) FRB_LAUNCH_DELTA(16, 4);
