@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(512) gated_delta_rule_kernel(DeltaParams p) {
         for (int c = 0; c < C; ++c) S[i][c] = (live[c] && row < dim) ? s_in[(size_t)row * vdim + j + c] : 0.f;
     }
     const float rate = expf(p.a_log[h]), dt_bias = p.dt_bias[h];
-    const float q_scale = rsqrtf((float)dim);
+    const float q_scale = 1.0f / sqrtf((float)dim);
     for (int i = threadIdx.x; i < 2 * DELTA_TOKENS * row_floats; i += blockDim.x) sm[i] = 0.f;       // the padding stays zero
 
     for (int n = 0; n < chunks; ++n) {
