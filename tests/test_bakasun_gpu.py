@@ -630,6 +630,25 @@ def test_unequal_requests_in_one_batch_then_decoded_together_over_reused_slots(n
         through(name, dtype, requests, steps, seeds, f"batch, turn {turn}")
 
 
+def test_the_fused_norm_against_its_three_kernels():
+    """The output norm, the sum and the next norm as one kernel, and as the deferred update made a tensor, normed, added and
+    normed by kernels of their own: the same logits up to float32 rounding."""
+    import fieldrun_b200.parts.norm as norm_part
+    name, length = "A", 150
+    ids = request_tokens(name, length, 11)
+    lm = loaded(name, "float32", record_steps=False)
+    results = []
+    for fused in (True, False):
+        kept, norm_part.FUSED_OUTPUT_NORM = norm_part.FUSED_OUTPUT_NORM, fused
+        try:
+            got, _ = run_schedule(lm, {"r": ids}, [[("r", 0, 100)]] + [[("r", p, p + 1)] for p in range(100, length)])
+        finally:
+            norm_part.FUSED_OUTPUT_NORM = kept
+        results.append(got["r"])
+    model_close(results[0], plain_run(name, length, 11)[0], "float32", "fused")
+    model_close(results[1], plain_run(name, length, 11)[0], "float32", "three kernels")
+
+
 def test_a_long_sequence_decoded_for_hundreds_of_tokens():
     name, length, tail = "B", 700, 400
     steps = [[("r", 0, length - tail)]] + [[("r", p, p + 1)] for p in range(length - tail, length)]
